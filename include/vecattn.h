@@ -1,0 +1,160 @@
+/* vecattn.h -- C ABI of libvecattn.so: the VecAttention prefill path on NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes, launches its kernels on the stream it is
+ * given, allocates no device memory, performs no host synchronisation and returns an int
+ * status (0 = ok, negative = error, see va_status_string).  All tensor pointers are device
+ * pointers.  Citations name files of the reference project (anminliu/VecAttention) whose
+ * interface each entry point stands in for.
+ *
+ * Tensor layout: 4-d tensors are (batch, heads, sequence, head_dim) with head_dim = 128, the
+ * innermost stride 1 and the other three strides given in elements, so both (B,H,S,D) and
+ * transposed (B,S,H,D) storage can be passed without a copy.  Rows must be 16-byte aligned.
+ */
+#ifndef VECATTN_H_
+#define VECATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* va_stream_t; /* a cudaStream_t */
+
+enum {
+  VA_OK = 0,
+  VA_ERR_NULL = -1,      /* a required pointer is NULL */
+  VA_ERR_DTYPE = -2,     /* dtype is neither VA_BF16 nor VA_FP16 */
+  VA_ERR_SHAPE = -3,     /* unsupported or inconsistent sizes */
+  VA_ERR_ALIGN = -4,     /* pointer or stride not 16-byte aligned */
+  VA_ERR_CAPACITY = -5,  /* index capacity or workspace too small */
+  VA_ERR_CUDA = -6,      /* a CUDA call failed (launch error) */
+  VA_ERR_PARAM = -7      /* parameter combination the reference also rejects */
+};
+
+enum { VA_BF16 = 0, VA_FP16 = 1 };
+
+/* bit set in a device status word by the selection kernel when a row kept more keys than
+ * the index capacity (indices beyond the capacity are dropped, the count stays exact) */
+enum { VA_STATUS_OVERFLOW = 1 };
+
+typedef struct {
+  const void* ptr;
+  int64_t stride_b, stride_h, stride_s; /* elements */
+} va_tensor4;
+
+typedef struct {
+  void* ptr;
+  int64_t stride_b, stride_h, stride_s;
+} va_tensor4_out;
+
+/* ---- mean pooling of Q -------------------------------------------------------------------
+ * Replaces average_vector(q, block_size, use_triton=True), spattn/src/utils.py:340-351 and the
+ * Triton kernel bnhd_pool_kernel, spattn/src/utils.py:8-83.  out[b,h,t,:] = mean over the rows
+ * of query tile t (a ragged last tile divides by its own row count), summed in fp32 as a
+ * balanced binary tree and rounded to the input dtype.  out is (B,H,ceil(S/pq),D) contiguous. */
+typedef struct {
+  int32_t dtype, batch, heads, seq_len, head_dim, pq;
+  va_tensor4 q;
+  void* out;
+} va_pool_args;
+int va_pool_q(const va_pool_args* args, va_stream_t stream);
+
+/* ---- important-vector (key column) selection -------------------------------------------------
+ * Replaces fuse_qk_softmax_minp_wo_causal(avg_q_chunk, k, avg_q_chunk_offset, gap, causal,
+ * q_pooling_size, k_local_size, wo_initial, group_k_block),
+ * spattn/src/kernels/vecattention_kernels.py:59-181, and its two Triton kernels (:206-345).
+ *   avg_q      (B,H,nq,D) contiguous pooled queries of one chunk (unscaled; scaled by 1/sqrt(D)
+ *              in fp32 and re-rounded inside, as the reference kernel does, :244-245)
+ *   k          (B,Hkv,Sk,D), H % Hkv == 0 (the reference requires Hkv == H, :92; Hkv < H behaves
+ *              as the reference does on repeat_kv-expanded keys)
+ *   tile_offset index of the chunk's first query tile in the whole sequence (:233)
+ *   gap / gaps  -ln(threshold): one float, or if gaps != NULL a device array read as
+ *              gaps[b * gaps_stride_b + h] (the reference reads gaps[b*H + h], :301-302)
+ *   compat_bsq  the reference's Triton program height (64 for every shipped causal config).
+ *              Causal only: the first pooled row of every compat_bsq rows of the chunk loses the
+ *              key blocks that start inside the tile before its diagonal tile, except the first
+ *              (truncating division at :260).  0 = strict rule (all keys before the diagonal tile).
+ *   col_count  (B,H,nq) int32 out; col_idx (B,H,nq,capacity) int32 out, every row ascending.
+ *              capacity >= Sk can never overflow.  status (optional) receives VA_STATUS_* bits.
+ * Unlike the reference no buffer is zero-filled: entries of col_idx past col_count are not written. */
+typedef struct {
+  int32_t dtype, batch, heads, kv_heads, nq, sk, head_dim;
+  int32_t pq, bk, group_k_block;
+  int32_t causal, wo_initial, compat_bsq, tile_offset;
+  const void* avg_q;
+  va_tensor4 k;
+  float gap;
+  const float* gaps;
+  int64_t gaps_stride_b;
+  int32_t* col_count;
+  int32_t* col_idx;
+  int64_t capacity;
+  int32_t* status;
+} va_select_args;
+int va_select(const va_select_args* args, va_stream_t stream);
+
+/* ---- vector-sparse flash attention --------------------------------------------------------------
+ * Replaces vllm_flash_attn.sparse_attn_func(q, k, v, q_pooling_size, block_count, block_offset,
+ * column_count, column_index, return_softmax_lse=False, causal=...), called at
+ * spattn/src/VecAttention.py:110-121 (package vllm-flash-attn 2.7.2.post1, a fork whose source is
+ * not in the reference tree).  For query tile t (pq rows): out = softmax(q K_t^T * scale) V_t over
+ * K_t = 64-key blocks starting at blk_idx[b,h,t,:blk_count] plus keys col_idx[b,h,t,:col_count]
+ * (the two sets must be disjoint).  causal: key <= q_offset + row, applied per element.
+ *   q, out     (B,H,Sq,D) rows q_offset .. q_offset+Sq-1 of the sequence;  k, v (B,Hkv,Sk,D)
+ *   blk_count  (B,H,nq) int32, blk_idx (B,H,nq,blk_stride) int32 (may be NULL when no blocks)
+ *   col_count  (B,H,nq) int32, col_idx (B,H,nq,col_stride) int32
+ *   softmax_scale 0 selects 1/sqrt(D).  A tile with no key at all writes zeros. */
+typedef struct {
+  int32_t dtype, batch, heads, kv_heads, sq, sk, head_dim, pq;
+  int32_t causal, q_offset;
+  va_tensor4 q, k, v;
+  va_tensor4_out out;
+  const int32_t* blk_count;
+  const int32_t* blk_idx;
+  int64_t blk_stride;
+  const int32_t* col_count;
+  const int32_t* col_idx;
+  int64_t col_stride;
+  float softmax_scale;
+} va_attn_args;
+int va_sparse_attn(const va_attn_args* args, va_stream_t stream);
+
+/* ---- dense 64-key block tables -----------------------------------------------------------------
+ * Replaces the table construction in VecAttention_prefill, spattn/src/VecAttention.py:62-92:
+ * causal -> sink blocks + diagonal blocks per tile, non-causal -> none.
+ * blk_count (B,H,nq), blk_idx (B,H,nq,max(1, 2*pq/64)) int32 contiguous. */
+int va_block_tables(int32_t batch, int32_t heads, int32_t seq_len, int32_t pq, int32_t causal,
+                    int32_t* blk_count, int32_t* blk_idx, va_stream_t stream);
+
+/* ---- the whole operator -----------------------------------------------------------------------
+ * Replaces VecAttention_prefill(query_states, key_states, value_states, threshold,
+ * q_pooling_size, k_local_size, group_k_block, causal, chunk_size),
+ * spattn/src/VecAttention.py:10-123: pooling, selection and sparse attention for every chunk,
+ * enqueued on one stream with no host synchronisation.  workspace must hold
+ * va_prefill_workspace_bytes() bytes and be 256-byte aligned.  col_count_out (optional,
+ * (B,H,ceil(Sq/pq)) int32) receives the per-tile selection counts. */
+typedef struct {
+  int32_t dtype, batch, heads, kv_heads, sq, sk, head_dim;
+  int32_t pq, bk, group_k_block, causal, chunk_size, compat_bsq;
+  va_tensor4 q, k, v;
+  va_tensor4_out out;
+  float gap;
+  const float* gaps;
+  int64_t gaps_stride_b;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* col_count_out;
+  int32_t* status;
+} va_prefill_args;
+int va_prefill_workspace_bytes(const va_prefill_args* args, size_t* bytes);
+int va_prefill(const va_prefill_args* args, va_stream_t stream);
+
+const char* va_status_string(int code);
+int va_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VECATTN_H_ */

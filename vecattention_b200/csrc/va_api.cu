@@ -1,0 +1,227 @@
+// C ABI of libvecattn.so: argument validation, workspace carving and kernel launches.
+// No device allocation, no host synchronisation, no C++ exception crosses this boundary.
+#include "va_common.cuh"
+
+namespace va {
+int pool_q(const va_pool_args& a, cudaStream_t stream);
+int select(const va_select_args& a, cudaStream_t stream);
+int sparse_attn(const va_attn_args& a, cudaStream_t stream);
+
+// dense-block tables of query tiles [tile_off, tile_off + nqc) written as a contiguous (BH, nqc) slice
+__global__ void block_tables_kernel(int bh, int seq_len, int pq, int causal, int tile_off, int nqc,
+                                    int32_t* __restrict__ blk_count, int32_t* __restrict__ blk_idx) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= bh * nqc) return;
+  const int n = pq / 64;
+  const int width = causal ? 2 * n : 1;
+  const int t = tile_off + i % nqc;
+  const int nq = (seq_len + pq - 1) / pq;
+  int32_t* row = blk_idx + (int64_t)i * width;
+  if (!causal) {
+    blk_count[i] = 0;
+    row[0] = 0;
+    return;
+  }
+  int cnt = 2 * n;
+  if (t == 0) cnt = (min(seq_len, pq) + 63) / 64;
+  else if (t == nq - 1 && seq_len % pq != 0) cnt = n + (seq_len - (seq_len / pq) * pq + 63) / 64;
+  blk_count[i] = cnt;
+  for (int j = 0; j < n; ++j) {
+    row[j] = j * 64;
+    row[n + j] = t * pq + j * 64;
+  }
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline bool strides_ok(int64_t sb, int64_t sh, int64_t ss) { return sb % 8 == 0 && sh % 8 == 0 && ss % 8 == 0; }
+template <class TT> static inline int check_tensor(const TT& t) {
+  if (!t.ptr) return VA_ERR_NULL;
+  if (!aligned16(t.ptr) || !strides_ok(t.stride_b, t.stride_h, t.stride_s)) return VA_ERR_ALIGN;
+  return VA_OK;
+}
+static inline bool bk_ok(int bk) { return bk == 16 || bk == 32 || bk == 64 || bk == 128; }
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct PrefillPlan {
+  int nq_total, nqc_max, blk_width;
+  int64_t capacity;
+  size_t off_avg, off_cnt, off_idx, off_bcnt, off_bidx, total;
+};
+
+static int plan_prefill(const va_prefill_args& a, PrefillPlan& pl) {
+  if (a.dtype != VA_BF16 && a.dtype != VA_FP16) return VA_ERR_DTYPE;
+  if (a.head_dim != kHeadDim || a.batch <= 0 || a.heads <= 0 || a.kv_heads <= 0 || a.sq <= 0 || a.sk <= 0)
+    return VA_ERR_SHAPE;
+  if (a.heads % a.kv_heads != 0 || a.heads > 65535 || a.batch > 65535) return VA_ERR_SHAPE;
+  if (a.pq != 64 && a.pq != 128) return VA_ERR_PARAM;                    // VecAttention.py:44
+  if (a.chunk_size <= 0 || a.chunk_size % a.pq != 0) return VA_ERR_PARAM;  // VecAttention.py:43
+  if (!bk_ok(a.bk) || a.group_k_block <= 0) return VA_ERR_SHAPE;
+  if (a.causal && a.pq % a.bk != 0) return VA_ERR_PARAM;                 // vecattention_kernels.py:129
+  if (a.causal && a.sq != a.sk) return VA_ERR_PARAM;
+  const size_t bh = (size_t)a.batch * a.heads;
+  const int chunk = a.chunk_size < a.sq ? a.chunk_size : a.sq;
+  pl.nq_total = (a.sq + a.pq - 1) / a.pq;
+  pl.nqc_max = (chunk + a.pq - 1) / a.pq;
+  pl.blk_width = a.causal ? 2 * (a.pq / 64) : 1;
+  pl.capacity = (a.sk + 3) / 4 * 4;
+  size_t off = 0;
+  pl.off_avg = off;  off = align_up(off + bh * pl.nqc_max * kHeadDim * 2, 256);
+  pl.off_cnt = off;  off = align_up(off + bh * pl.nqc_max * 4, 256);
+  pl.off_bcnt = off; off = align_up(off + bh * pl.nqc_max * 4, 256);
+  pl.off_bidx = off; off = align_up(off + bh * pl.nqc_max * pl.blk_width * 4, 256);
+  pl.off_idx = off;  off = align_up(off + bh * pl.nqc_max * (size_t)pl.capacity * 4, 256);
+  pl.total = off;
+  return VA_OK;
+}
+}  // namespace va
+
+using namespace va;
+
+extern "C" {
+
+int va_version(void) { return 100; }
+
+const char* va_status_string(int code) {
+  switch (code) {
+    case VA_OK: return "ok";
+    case VA_ERR_NULL: return "a required pointer is NULL";
+    case VA_ERR_DTYPE: return "dtype must be VA_BF16 or VA_FP16";
+    case VA_ERR_SHAPE: return "unsupported or inconsistent sizes (head_dim must be 128, k_local_size one of 16/32/64/128, heads a multiple of kv_heads)";
+    case VA_ERR_ALIGN: return "pointers and strides must be multiples of 16 bytes";
+    case VA_ERR_CAPACITY: return "index capacity or workspace too small";
+    case VA_ERR_CUDA: return "CUDA launch failed";
+    case VA_ERR_PARAM: return "parameters rejected (q_pooling_size must be 64 or 128, chunk_size a multiple of it, causal needs q_pooling_size % k_local_size == 0 and Sq == Sk)";
+    default: return "unknown status";
+  }
+}
+
+int va_pool_q(const va_pool_args* a, va_stream_t stream) {
+  if (!a || !a->out) return VA_ERR_NULL;
+  if (a->dtype != VA_BF16 && a->dtype != VA_FP16) return VA_ERR_DTYPE;
+  if (a->head_dim != kHeadDim || a->batch <= 0 || a->heads <= 0 || a->seq_len <= 0 || a->heads > 65535 || a->batch > 65535)
+    return VA_ERR_SHAPE;
+  if (a->pq != 64 && a->pq != 128) return VA_ERR_PARAM;
+  if (int rc = check_tensor(a->q)) return rc;
+  if (!aligned16(a->out)) return VA_ERR_ALIGN;
+  return pool_q(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int va_select(const va_select_args* a, va_stream_t stream) {
+  if (!a || !a->avg_q || !a->col_count || !a->col_idx) return VA_ERR_NULL;
+  if (a->dtype != VA_BF16 && a->dtype != VA_FP16) return VA_ERR_DTYPE;
+  if (a->head_dim != kHeadDim || a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->nq <= 0 || a->sk <= 0)
+    return VA_ERR_SHAPE;
+  if (a->heads % a->kv_heads != 0 || a->kv_heads > 65535 || a->batch > 65535) return VA_ERR_SHAPE;
+  if (!bk_ok(a->bk) || a->group_k_block <= 0 || a->pq <= 0) return VA_ERR_SHAPE;
+  if ((a->causal || a->wo_initial) && a->pq % a->bk != 0) return VA_ERR_PARAM;
+  if (a->capacity <= 0) return VA_ERR_CAPACITY;
+  if (a->compat_bsq < 0 || a->tile_offset < 0) return VA_ERR_SHAPE;
+  if (int rc = check_tensor(a->k)) return rc;
+  if (!aligned16(a->avg_q)) return VA_ERR_ALIGN;
+  return select(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int va_sparse_attn(const va_attn_args* a, va_stream_t stream) {
+  if (!a || !a->col_count || !a->col_idx) return VA_ERR_NULL;
+  if (a->blk_count && !a->blk_idx) return VA_ERR_NULL;
+  if (a->dtype != VA_BF16 && a->dtype != VA_FP16) return VA_ERR_DTYPE;
+  if (a->head_dim != kHeadDim || a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->sq <= 0 || a->sk <= 0)
+    return VA_ERR_SHAPE;
+  if (a->heads % a->kv_heads != 0 || a->heads > 65535 || a->batch > 65535) return VA_ERR_SHAPE;
+  if (a->pq != 64 && a->pq != 128) return VA_ERR_PARAM;
+  if (a->q_offset < 0 || a->col_stride <= 0) return VA_ERR_SHAPE;
+  if (int rc = check_tensor(a->q)) return rc;
+  if (int rc = check_tensor(a->k)) return rc;
+  if (int rc = check_tensor(a->v)) return rc;
+  if (int rc = check_tensor(a->out)) return rc;
+  return sparse_attn(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int va_block_tables(int32_t batch, int32_t heads, int32_t seq_len, int32_t pq, int32_t causal, int32_t* blk_count,
+                    int32_t* blk_idx, va_stream_t stream) {
+  if (!blk_count || !blk_idx) return VA_ERR_NULL;
+  if (batch <= 0 || heads <= 0 || seq_len <= 0) return VA_ERR_SHAPE;
+  if (pq != 64 && pq != 128) return VA_ERR_PARAM;
+  const int nq = (seq_len + pq - 1) / pq;
+  const int64_t n = (int64_t)batch * heads * nq;
+  if (n > 0x7fffffff) return VA_ERR_SHAPE;
+  block_tables_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      batch * heads, seq_len, pq, causal, 0, nq, blk_count, blk_idx);
+  return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
+}
+
+int va_prefill_workspace_bytes(const va_prefill_args* a, size_t* bytes) {
+  if (!a || !bytes) return VA_ERR_NULL;
+  PrefillPlan pl;
+  if (int rc = plan_prefill(*a, pl)) return rc;
+  *bytes = pl.total;
+  return VA_OK;
+}
+
+int va_prefill(const va_prefill_args* a, va_stream_t stream_) {
+  if (!a || !a->workspace) return VA_ERR_NULL;
+  PrefillPlan pl;
+  if (int rc = plan_prefill(*a, pl)) return rc;
+  if (a->workspace_bytes < pl.total) return VA_ERR_CAPACITY;
+  if ((reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0) return VA_ERR_ALIGN;
+  if (int rc = check_tensor(a->q)) return rc;
+  if (int rc = check_tensor(a->k)) return rc;
+  if (int rc = check_tensor(a->v)) return rc;
+  if (int rc = check_tensor(a->out)) return rc;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  unsigned char* ws = static_cast<unsigned char*>(a->workspace);
+  void* avg = ws + pl.off_avg;
+  int32_t* cnt = reinterpret_cast<int32_t*>(ws + pl.off_cnt);
+  int32_t* idx = reinterpret_cast<int32_t*>(ws + pl.off_idx);
+  int32_t* bcnt = reinterpret_cast<int32_t*>(ws + pl.off_bcnt);
+  int32_t* bidx = reinterpret_cast<int32_t*>(ws + pl.off_bidx);
+  const int bh = a->batch * a->heads;
+  const size_t esz = 2;
+
+  for (int i = 0; i < a->sq; i += a->chunk_size) {  // VecAttention.py:94
+    const int sqc = (a->sq - i) < a->chunk_size ? (a->sq - i) : a->chunk_size;
+    const int nqc = (sqc + a->pq - 1) / a->pq;
+    va_tensor4 qc = a->q;
+    qc.ptr = static_cast<const unsigned char*>(a->q.ptr) + (size_t)i * a->q.stride_s * esz;
+    va_tensor4_out oc = a->out;
+    oc.ptr = static_cast<unsigned char*>(a->out.ptr) + (size_t)i * a->out.stride_s * esz;
+
+    va_pool_args pa{a->dtype, a->batch, a->heads, sqc, a->head_dim, a->pq, qc, avg};
+    if (int rc = pool_q(pa, stream)) return rc;
+
+    va_select_args sa{};
+    sa.dtype = a->dtype; sa.batch = a->batch; sa.heads = a->heads; sa.kv_heads = a->kv_heads;
+    sa.nq = nqc; sa.sk = a->sk; sa.head_dim = a->head_dim;
+    sa.pq = a->pq; sa.bk = a->bk; sa.group_k_block = a->group_k_block;
+    sa.causal = a->causal; sa.wo_initial = a->causal;  // VecAttention.py:101
+    sa.compat_bsq = a->compat_bsq; sa.tile_offset = i / a->pq;
+    sa.avg_q = avg; sa.k = a->k; sa.gap = a->gap; sa.gaps = a->gaps; sa.gaps_stride_b = a->gaps_stride_b;
+    sa.col_count = cnt; sa.col_idx = idx; sa.capacity = pl.capacity; sa.status = a->status;
+    if (int rc = select(sa, stream)) return rc;
+
+    block_tables_kernel<<<(bh * nqc + 255) / 256, 256, 0, stream>>>(bh, a->sq, a->pq, a->causal, i / a->pq, nqc, bcnt,
+                                                                    bidx);
+    if (cudaGetLastError() != cudaSuccess) return VA_ERR_CUDA;
+
+    va_attn_args aa{};
+    aa.dtype = a->dtype; aa.batch = a->batch; aa.heads = a->heads; aa.kv_heads = a->kv_heads;
+    aa.sq = sqc; aa.head_dim = a->head_dim; aa.pq = a->pq;
+    const int64_t kend = (int64_t)i + a->chunk_size;
+    aa.sk = a->causal ? (int)(kend < a->sk ? kend : a->sk) : a->sk;  // VecAttention.py:107-108
+    aa.causal = a->causal; aa.q_offset = i;
+    aa.q = qc; aa.k = a->k; aa.v = a->v; aa.out = oc;
+    aa.blk_count = bcnt; aa.blk_idx = bidx; aa.blk_stride = pl.blk_width;
+    aa.col_count = cnt; aa.col_idx = idx; aa.col_stride = pl.capacity;
+    aa.softmax_scale = 0.f;
+    if (int rc = sparse_attn(aa, stream)) return rc;
+
+    if (a->col_count_out) {
+      if (cudaMemcpy2DAsync(a->col_count_out + i / a->pq, (size_t)pl.nq_total * 4, cnt, (size_t)nqc * 4,
+                            (size_t)nqc * 4, bh, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+        return VA_ERR_CUDA;
+    }
+  }
+  return VA_OK;
+}
+
+}  // extern "C"
