@@ -1,0 +1,426 @@
+#!/usr/bin/env python
+"""Benchmark of the VecAttention prefill hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|mini]
+                    [--scaling weak|strong] [--impl graft|reference]
+
+A step is one call of ``VecAttention_prefill`` (pool -> select -> vector-sparse attention) over
+one layer's q/k/v of the named synthetic workload.  ``value`` is effective TFLOP/s: the FLOPs of
+the selected (query tile, key) pairs only, 4 * rows * head_dim per pair, summed over all ranks,
+divided by the slowest rank's device time.  One JSON line is printed by rank 0.
+
+Under ``torchrun`` (N > 1) every rank drives one GPU.  ``--scaling weak`` (default): every rank
+runs the whole single-GPU workload on its own draw of the data (no communication at all);
+``--scaling strong``: the heads of one layer are sharded across the ranks.
+
+``--impl reference`` times the CPU restatement of the reference's PyTorch path (the oracle) with
+all host threads on a bounded sample of the same workload; rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu
+# capture summarised under profiles/ (workload -> bytes); None until a capture exists
+NCU_TRAFFIC_BYTES = {}
+D = 128
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["_source"] = "fallback"
+    return p
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-f", self.path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        try:
+            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
+            os.unlink(self.path)
+        except (OSError, TypeError):
+            return out
+        sm, reasons = [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                out["sm_max_mhz"] = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for n, val in zip(names, r[2:6]):
+                if val.strip().lower() == "active":
+                    reasons.add(n)
+        if sm:
+            out["sm_mhz"] = statistics.median(sm)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def effective_flops(counts: torch.Tensor, wl, blocks_per_tile=None) -> float:
+    """4 * rows * D FLOPs per (query tile, key) pair; a ragged last tile counts its real rows."""
+    pq = wl.q_pooling_size
+    rows = torch.full((wl.nq,), pq, dtype=torch.float64, device=counts.device)
+    rows[-1] = wl.seq_len - (wl.nq - 1) * pq
+    keys = counts.to(torch.float64)
+    if blocks_per_tile is not None:
+        keys = keys + blocks_per_tile.to(torch.float64) * 64
+    return float((keys * rows.view(1, 1, -1)).sum()) * 4.0 * D
+
+
+def time_cuda(fn, warmup: int, iters: int) -> float:
+    """Mean milliseconds per call on the current stream (CUDA events, synchronised both sides)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def cpu_sample(name: str, threshold: float, tiles: int, sample_seed: int = 0):
+    """Inputs of the bounded CPU sample: one head, the first ``tiles`` query tiles, all keys."""
+    from vecattention_b200.synth import make_workload
+    wl = make_workload(name, device="cpu", heads=range(0, 1), sample_seed=sample_seed)
+    if wl.heads != 1:  # GQA: first KV group's first head
+        wl.q = wl.q[:, :1]
+    rows = min(wl.seq_len, tiles * wl.q_pooling_size)
+    return wl, wl.q[:, :, :rows].contiguous()
+
+
+def run_cpu_sample(wl, q_rows, threshold: float):
+    """One pass of the oracle over the sample; returns (seconds, effective FLOPs)."""
+    from oracle import vecattn_oracle as O
+    t0 = time.perf_counter()
+    if wl.causal:
+        out, sel = O.vecattention_prefill(q_rows, wl.k[:, :1, : q_rows.shape[2]], wl.v[:, :1, : q_rows.shape[2]],
+                                          threshold, wl.q_pooling_size, wl.k_local_size, wl.group_k_block, True,
+                                          wl.chunk_size, return_selection=True)
+    else:
+        out, sel = O.vecattention_prefill(q_rows, wl.k[:, :1], wl.v[:, :1], threshold, wl.q_pooling_size,
+                                          wl.k_local_size, wl.group_k_block, False, wl.chunk_size,
+                                          return_selection=True)
+    dt = time.perf_counter() - t0
+    pq = wl.q_pooling_size
+    flops = 0.0
+    t = 0
+    for cc, _ in sel:
+        for c in cc.flatten().tolist():
+            rows = min(pq, q_rows.shape[2] - t * pq)
+            flops += 4.0 * D * rows * c
+            t += 1
+    return dt, flops
+
+
+def reference_arm(args):
+    """The reference's CPU/PyTorch path (oracle restatement) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    thr = args.threshold if args.threshold else 0.5
+    wl, q_rows = cpu_sample(args.workload, thr, args.cpu_tiles)
+    if not args.threshold:
+        from oracle import vecattn_oracle as O
+        thr = _calibrate_cpu(wl, q_rows, O)
+    for _ in range(max(1, min(args.warmup, 1))):
+        run_cpu_sample(wl, q_rows, thr)
+    secs, flops = [], 0.0
+    for _ in range(args.steps):
+        dt, flops = run_cpu_sample(wl, q_rows, thr)
+        secs.append(dt)
+    t = sum(secs) / len(secs)
+    value = flops / t / 1e12
+    sample = f"1 head x {q_rows.shape[2] // wl.q_pooling_size} query tiles x all {wl.seq_len} keys of {wl.name} per step"
+    line = {
+        "impl": "reference", "metric": "vecattention_prefill_effective_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl.name, "threshold": thr, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def _calibrate_cpu(wl, q_rows, O) -> float:
+    avg = O.pool_q(q_rows, wl.q_pooling_size)
+    nq = avg.shape[2]
+    pq = wl.q_pooling_size
+    elig = sum(max(0, min(wl.seq_len, g * pq) - pq) for g in range(nq)) if wl.causal else nq * wl.seq_len
+    lo, hi = 1e-9, 1.0
+    kk = wl.k[:, :1]
+    for _ in range(12):
+        mid = math.sqrt(lo * hi)
+        cnt, _ = O.select_columns(avg, kk, 0, -math.log(mid + 1e-9), wl.causal, pq, wl.k_local_size,
+                                  wl.causal, wl.group_k_block)
+        if float(cnt.sum()) / max(elig, 1) > wl.keep:
+            lo = mid
+        else:
+            hi = mid
+    return math.sqrt(lo * hi)
+
+
+def graft_arm(args):
+    import torch.distributed as dist
+    import vecattention_b200 as va
+    from vecattention_b200 import api
+    from vecattention_b200.sharding import local_slices
+    from vecattention_b200.synth import calibrate_threshold, make_workload
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path for the product arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    from vecattention_b200.synth import CONFIGS
+    cfg = CONFIGS[args.workload]
+    if args.scaling == "strong" and world > 1:
+        hs, _ = local_slices(cfg["heads"], cfg["kv_heads"], rank, world)
+        wl = make_workload(args.workload, device=dev, heads=range(hs.start, hs.stop))
+    else:
+        wl = make_workload(args.workload, device=dev, sample_seed=rank)
+    pq, bk, g, chunk = wl.q_pooling_size, wl.k_local_size, wl.group_k_block, wl.chunk_size
+
+    # ---- threshold calibrated to the configuration's keep ratio (untimed) ----
+    if args.threshold:
+        thr = args.threshold
+    else:
+        avg_all = va.average_vector(wl.q, pq)
+        rep = wl.heads // wl.kv_heads
+
+        def counts_at(th, hslice):
+            kv = slice(hslice.start // rep, max(1, hslice.stop // rep))
+            cnt, _ = va.fuse_qk_softmax_minp_wo_causal(avg_all[:, hslice].contiguous(), wl.k[:, kv], 0,
+                                                       -math.log(th + 1e-9), wl.causal, pq, bk, wo_initial=wl.causal,
+                                                       group_k_block=g, trim=False, capacity=4)
+            return cnt
+        thr = calibrate_threshold(wl, counts_at)
+        del avg_all
+    out = torch.empty_like(wl.q)
+
+    def step():
+        va.VecAttention_prefill(wl.q, wl.k, wl.v, thr, pq, bk, g, wl.causal, chunk, out=out)
+
+    _, counts = va.VecAttention_prefill(wl.q, wl.k, wl.v, thr, pq, bk, g, wl.causal, chunk, return_selection=True)
+    bcnt, bidx = api.block_tables(wl.batch, wl.heads, wl.seq_len, pq, wl.causal, dev)
+    flops = effective_flops(counts, wl, bcnt if wl.causal else None)
+    kept = float(counts.sum()) / (wl.eligible_pairs_per_head() * wl.heads * wl.batch)
+
+    # ---- timed region: exactly K steps, device time, max over ranks ----
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    with ClockSampler(local_rank) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = clk.summary()
+    t = torch.tensor([ms_total, flops], dtype=torch.float64, device=dev)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms_total, flops_all = float(tmax[0]), float(tsum[1])
+    else:
+        flops_all = flops
+    ms_step = ms_total / args.steps
+    value = flops_all / (ms_step * 1e-3) / 1e12
+    n_chunks = math.ceil(wl.seq_len / chunk)
+    launches = args.steps * n_chunks * 4  # pool + select + block tables + attention per chunk
+
+    line = None
+    if rank == 0:
+        peaks = load_peaks()
+        # ---- per-kernel times (same entry points the operator uses), rank 0 ----
+        avg = va.average_vector(wl.q, pq)
+        t_pool = time_cuda(lambda: va.average_vector(wl.q, pq), 3, 10)
+        stage = {"pool_ms": t_pool}
+        nqc = math.ceil(min(chunk, wl.seq_len) / pq)
+        sel_ms, att_ms = 0.0, 0.0
+        for i in range(0, wl.seq_len, chunk):
+            t0, t1 = i // pq, min(wl.nq, (i + chunk) // pq)
+            avg_c = avg[:, :, t0:t1].contiguous()
+            gap = -math.log(thr + 1e-9)
+            sel = lambda: va.fuse_qk_softmax_minp_wo_causal(avg_c, wl.k, t0, gap, wl.causal, pq, bk,
+                                                            wo_initial=wl.causal, group_k_block=g, trim=False)
+            cc, ci = sel()
+            sel_ms += time_cuda(sel, 2, 5)
+            sk_eff = min(wl.seq_len, i + chunk) if wl.causal else wl.seq_len
+            qc = wl.q[:, :, i:i + chunk]
+            oc = out[:, :, i:i + chunk]
+            bc, bi = bcnt[:, :, t0:t1].contiguous(), bidx[:, :, t0:t1].contiguous()
+            att = lambda: api._sparse_attn_bhsd(qc, wl.k[:, :, :sk_eff], wl.v[:, :, :sk_eff], pq, bc, bi, cc, ci,
+                                                wl.causal, q_offset=i, out=oc)
+            att_ms += time_cuda(att, 2, 5)
+            del cc, ci
+        stage.update(select_ms=sel_ms, attn_ms=att_ms)
+        esz = 2
+        kept_total = float(counts.sum())
+        sel_bytes = (wl.q.numel() + wl.k.numel()) * esz + 4 * kept_total + 4 * counts.numel()
+        peak_tf = peaks["bf16_tflops"]
+        achieved_tf = flops / (att_ms * 1e-3) / 1e12
+        roofline = {"kernel": "sparse_attn_kernel", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
+                    "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
+                    "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "peak_source": peaks["_source"] + " burst"}
+        sel_gbs = sel_bytes / ((t_pool + sel_ms) * 1e-3) / 1e9
+        roofline_select = {"kernel": "pool_q_kernel+select_kernel", "bound": "hbm", "achieved": sel_gbs,
+                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"],
+                           "algorithmic_bytes": sel_bytes, "peak_source": peaks["_source"]}
+
+        # ---- dense attention on the same GPU, for context (library kernel, one head group) ----
+        dense_ms = None
+        try:
+            hd = min(wl.heads, 4)
+            rep = wl.heads // wl.kv_heads
+            qd = wl.q[:, :hd]
+            kd = wl.k[:, : max(1, hd // rep)].repeat_interleave(min(rep, hd), dim=1)[:, :hd]
+            vd = wl.v[:, : max(1, hd // rep)].repeat_interleave(min(rep, hd), dim=1)[:, :hd]
+            f = lambda: torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, is_causal=wl.causal)
+            dense_ms = time_cuda(f, 1, 3) * wl.heads / hd
+        except Exception:  # the comparison is optional
+            dense_ms = None
+
+        # ---- end to end through the public API with host buffers ----
+        qh, kh, vh = (x.cpu().pin_memory() for x in (wl.q, wl.k, wl.v))
+        oh = torch.empty_like(qh).pin_memory()
+        qd_, kd_, vd_ = torch.empty_like(wl.q), torch.empty_like(wl.k), torch.empty_like(wl.v)
+
+        def e2e_step():
+            qd_.copy_(qh, non_blocking=True)
+            kd_.copy_(kh, non_blocking=True)
+            vd_.copy_(vh, non_blocking=True)
+            va.VecAttention_prefill(qd_, kd_, vd_, thr, pq, bk, g, wl.causal, chunk, out=out)
+            oh.copy_(out, non_blocking=True)
+        e2e_ms = time_cuda(e2e_step, 2, max(3, min(args.steps, 5)))
+        h2d = (qh.numel() + kh.numel() + vh.numel()) * esz
+        d2h = oh.numel() * esz
+        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "note": "single-GPU call with pinned host buffers (rank 0)"}
+
+        # ---- CPU baseline: the oracle on a bounded sample, host cores of this box ----
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        cwl, q_rows = cpu_sample(args.workload, thr, args.cpu_tiles)
+        run_cpu_sample(cwl, q_rows, thr)
+        reps, secs, cflops = 0, 0.0, 0.0
+        while secs < 10.0 and reps < 20:
+            dt, cflops = run_cpu_sample(cwl, q_rows, thr)
+            secs += dt
+            reps += 1
+        cpu_value = cflops * reps / secs / 1e12
+        cpu_baseline = {"value": cpu_value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                        "sample": f"1 head x {q_rows.shape[2] // pq} query tiles x all {wl.seq_len} keys of "
+                                  f"{wl.name}, {reps} passes, {secs:.1f} s"}
+
+        line = {
+            "metric": "vecattention_prefill_effective_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": wl.name, "batch": wl.batch, "heads": wl.heads, "kv_heads": wl.kv_heads,
+                       "seq_len": wl.seq_len, "head_dim": D, "causal": wl.causal, "q_pooling_size": pq,
+                       "k_local_size": bk, "group_k_block": g, "chunk_size": chunk, "threshold": thr,
+                       "keep_ratio": kept, "effective_flops_per_step_per_gpu": flops,
+                       "l2": "inputs larger than L2 (q+k+v = %.0f MB per GPU), no flush" %
+                             ((wl.q.numel() + 2 * wl.k.numel()) * esz / 1e6),
+                       "parallelism": ("replicated workload per GPU" if args.scaling == "weak" else "heads sharded")},
+            "ms_per_layer": ms_step, "stage_ms": stage, "dense_attention_ms": dense_ms,
+            "roofline": roofline, "roofline_select": roofline_select, "cpu_baseline": cpu_baseline,
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        }
+    barrier()
+    if world > 1:
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="graft", choices=["graft", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "mini"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--threshold", type=float, default=0.0, help="skip calibration and use this MinP threshold")
+    ap.add_argument("--cpu-tiles", type=int, default=64, help="query tiles in the bounded CPU sample")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "graft" else args.warmup
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        graft_arm(args)
+
+
+if __name__ == "__main__":
+    main()

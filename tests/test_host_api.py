@@ -1,0 +1,128 @@
+"""Host-side checks that need no GPU: the C-ABI library builds, loads and exports every symbol
+the header declares; argument validation returns error codes before anything is launched; the
+Python mirror raises where the reference asserts; workspace sizing."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib(built_library):
+    from vecattention_b200 import _lib
+    return _lib
+
+
+def test_header_symbols_are_exported(lib):
+    header = open(os.path.join(ROOT, "include", "vecattn.h")).read()
+    declared = set(re.findall(r"^(?:int|const char\*)\s+(va_\w+)\s*\(", header, flags=re.M))
+    assert declared == set(lib.EXPORTS), declared ^ set(lib.EXPORTS)
+    handle = lib.lib()
+    for name in declared:
+        assert hasattr(handle, name)
+    assert handle.va_version() >= 100
+    assert lib.status_string(0) == "ok"
+    for code in range(-7, 0):
+        assert "unknown" not in lib.status_string(code)
+
+
+def test_struct_layout_matches_header(lib):
+    # sizes of the C structs as the compiler lays them out (LP64): guards against drift between
+    # include/vecattn.h and the ctypes mirror
+    assert C.sizeof(lib.Tensor4) == 32
+    assert C.sizeof(lib.PoolArgs) == 24 + 32 + 8
+    assert C.sizeof(lib.SelectArgs) == 56 + 8 + 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8
+    assert C.sizeof(lib.AttnArgs) == 40 + 4 * 32 + 8 * 6 + 8
+    assert C.sizeof(lib.PrefillArgs) == 56 + 4 * 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8
+
+
+def test_validation_returns_codes_without_launching(lib):
+    h = lib.lib()
+    assert h.va_pool_q(None, None) == -1
+    assert h.va_select(None, None) == -1
+    assert h.va_sparse_attn(None, None) == -1
+    assert h.va_prefill(None, None) == -1
+    a = lib.PoolArgs(7, 1, 1, 64, 128, 64, lib.Tensor4(16, 0, 0, 128), 16)
+    assert h.va_pool_q(C.byref(a), None) == -2          # dtype
+    a.dtype = 0
+    a.head_dim = 64
+    assert h.va_pool_q(C.byref(a), None) == -3          # head_dim
+    a.head_dim = 128
+    a.pq = 32
+    assert h.va_pool_q(C.byref(a), None) == -7          # q_pooling_size
+    a.pq = 64
+    a.q.ptr = 8
+    assert h.va_pool_q(C.byref(a), None) == -4          # alignment
+    s = lib.SelectArgs()
+    s.avg_q, s.col_count, s.col_idx = 16, 16, 16
+    s.dtype, s.batch, s.heads, s.kv_heads, s.nq, s.sk, s.head_dim = 0, 1, 3, 2, 4, 256, 128
+    s.pq, s.bk, s.group_k_block, s.capacity = 64, 16, 1, 256
+    assert h.va_select(C.byref(s), None) == -3          # heads % kv_heads
+    s.heads = 4
+    s.bk = 24
+    assert h.va_select(C.byref(s), None) == -3          # k_local_size
+    s.bk = 128
+    s.causal = 1
+    assert h.va_select(C.byref(s), None) == -7          # causal needs pq % bk == 0
+    s.bk, s.capacity = 16, 0
+    assert h.va_select(C.byref(s), None) == -5          # capacity
+    assert h.va_block_tables(1, 1, 128, 64, 1, None, None, None) == -1
+
+
+def test_prefill_workspace_bytes(lib):
+    h = lib.lib()
+    a = lib.PrefillArgs()
+    a.dtype, a.batch, a.heads, a.kv_heads, a.sq, a.sk, a.head_dim = 0, 1, 32, 32, 32768, 32768, 128
+    a.pq, a.bk, a.group_k_block, a.causal, a.chunk_size, a.compat_bsq = 64, 16, 16, 0, 32768, 64
+    n = C.c_size_t(0)
+    assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n)) == 0
+    idx_bytes = 32 * 512 * 32768 * 4
+    assert idx_bytes <= n.value <= idx_bytes + 8 * 2 ** 20
+    a.chunk_size = 8192                                  # a smaller chunk bounds the index workspace
+    n2 = C.c_size_t(0)
+    assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n2)) == 0
+    assert n2.value < n.value / 3.9
+    a.chunk_size = 100
+    assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n2)) == -7
+    a.chunk_size, a.causal, a.sk = 8192, 1, 4096
+    assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n2)) == -7   # causal needs Sq == Sk
+    a.causal, a.workspace, a.workspace_bytes = 0, 256, 1024
+    a.q = a.k = a.v = a.out = lib.Tensor4(256, 0, 0, 128)
+    assert h.va_prefill(C.byref(a), None) == -5                           # workspace too small
+
+
+def test_python_mirror_raises_like_the_reference(built_library):
+    import vecattention_b200 as va
+    q = torch.zeros(1, 2, 256, 128, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError):
+        va.VecAttention_prefill(q, q, q, 0.5, 64, 16, 16, False, chunk_size=100)
+    with pytest.raises(AssertionError):
+        va.VecAttention_prefill(q, q, q, 0.5, 32, 16, 16, False, chunk_size=1024)
+    with pytest.raises(TypeError):
+        va.VecAttention_prefill(q, q, q, None, 64, 16, 16, False, chunk_size=1024)
+    # no CPU fallback: host tensors are refused, loudly
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        va.VecAttention_prefill(q, q, q, 0.5, 64, 16, 16, False, chunk_size=1024)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        va.average_vector(q, 64)
+
+
+def test_missing_library_fails_loudly(monkeypatch, built_library):
+    from vecattention_b200 import _lib
+    monkeypatch.setattr(_lib, "_LIB", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libvecattn.so")
+    with pytest.raises(RuntimeError, match="missing"):
+        _lib.lib()
+
+
+def test_product_package_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "vecattention_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("CPU oracle uses the same association", ""), f

@@ -228,13 +228,9 @@ __global__ void __launch_bounds__(PQ * 2) sparse_attn_kernel(const AttnParams p)
 template <int DT, int PQ>
 static int launch_attn_pq(const AttnParams& p, int batch, cudaStream_t stream) {
   constexpr size_t smem = attn_smem_bytes<PQ>();
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(sparse_attn_kernel<DT, PQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
-      return VA_ERR_CUDA;
-    configured = true;
-  }
+  // per-device attribute; setting it on every launch keeps multi-device processes correct
+  if (cudaFuncSetAttribute(sparse_attn_kernel<DT, PQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return VA_ERR_CUDA;
   dim3 grid(p.nq, p.heads, batch);
   sparse_attn_kernel<DT, PQ><<<grid, PQ * 2, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;

@@ -231,13 +231,9 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
 template <int DT, int BK>
 static int launch_select_bk(const SelectParams& p, int batch, cudaStream_t stream) {
   constexpr size_t smem = select_smem_bytes<BK>();
-  static bool configured = false;  // idempotent attribute; a benign race sets it twice
-  if (!configured) {
-    if (cudaFuncSetAttribute(select_kernel<DT, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
-      return VA_ERR_CUDA;
-    configured = true;
-  }
+  // per-device attribute; setting it on every launch keeps multi-device processes correct
+  if (cudaFuncSetAttribute(select_kernel<DT, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return VA_ERR_CUDA;
   const int nrows = p.rep * p.nq;
   dim3 grid((nrows + kSelRows - 1) / kSelRows, p.kv_heads, batch);
   select_kernel<DT, BK><<<grid, 128, smem, stream>>>(p);
