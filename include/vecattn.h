@@ -30,7 +30,8 @@ enum {
   VA_ERR_ALIGN = -4,     /* pointer or stride not 16-byte aligned */
   VA_ERR_CAPACITY = -5,  /* index capacity or workspace too small */
   VA_ERR_CUDA = -6,      /* a CUDA call failed (launch error) */
-  VA_ERR_PARAM = -7      /* parameter combination the reference also rejects */
+  VA_ERR_PARAM = -7,     /* parameter combination the reference also rejects */
+  VA_ERR_STATIC_SCRATCH = -8 /* va_prefill_static: the problem needs more than VA_STATIC_SCRATCH_BYTES */
 };
 
 enum { VA_BF16 = 0, VA_FP16 = 1 };
@@ -150,6 +151,33 @@ typedef struct {
 } va_prefill_args;
 int va_prefill_workspace_bytes(const va_prefill_args* args, size_t* bytes);
 int va_prefill(const va_prefill_args* args, va_stream_t stream);
+
+/* ---- the whole operator, for callers that must not allocate --------------------------------
+ * No counterpart in the reference (there every call allocates its temporaries through PyTorch).
+ *
+ * Who needs it: code that may not call cudaMalloc or a caching allocator at the point where the
+ * operator runs -- an inference server whose memory is handed out once at start-up and is owned
+ * by another component, a plugin running inside someone else's stream-ordered region, a host
+ * thread that is not allowed to touch the allocator's lock.  Such a caller still owns q, k, v and
+ * out; what it cannot provide is the scratch va_prefill wants in `workspace`.
+ *
+ * Same arguments and results as va_prefill; `workspace` and `workspace_bytes` are ignored.  The
+ * scratch is a fixed array of VA_STATIC_SCRATCH_BYTES bytes that is part of the library image:
+ * every GPU that loads the library carries it until the process exits.  A problem whose scratch
+ * (va_prefill_workspace_bytes) exceeds it is refused with VA_ERR_STATIC_SCRATCH and nothing is
+ * launched; the scratch is dominated by 4 * batch * heads * ceil(chunk_size / q_pooling_size) * Sk
+ * bytes of index lists, so a smaller chunk_size makes a larger problem fit.
+ *
+ * The function calls no cudaMalloc/cudaFree and no allocating library routine.  Its first call on
+ * a device looks up the array's device address (cudaGetSymbolAddress, with that device current);
+ * make that first call before any stream capture begins.
+ *
+ * All calls on a device share the one array and it keeps whatever the previous call left.  The
+ * kernels never read scratch they have not written in the same call, so nothing needs clearing;
+ * but two calls whose kernels overlap on the GPU (different streams, no ordering between them)
+ * race on it and corrupt each other's results.  Order such calls, or use va_prefill. */
+#define VA_STATIC_SCRATCH_BYTES (32u << 20)
+int va_prefill_static(const va_prefill_args* args, va_stream_t stream);
 
 const char* va_status_string(int code);
 int va_version(void);

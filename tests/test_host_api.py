@@ -26,7 +26,7 @@ def test_header_symbols_are_exported(lib):
         assert hasattr(handle, name)
     assert handle.va_version() >= 100
     assert lib.status_string(0) == "ok"
-    for code in range(-7, 0):
+    for code in range(-8, 0):
         assert "unknown" not in lib.status_string(code)
 
 

@@ -15,7 +15,8 @@ VA_STATUS_OVERFLOW = 1
 
 # every symbol include/vecattn.h declares
 EXPORTS = ("va_pool_q", "va_select", "va_sparse_attn", "va_block_tables", "va_prefill_workspace_bytes",
-           "va_prefill", "va_status_string", "va_version")
+           "va_prefill", "va_prefill_static", "va_status_string", "va_version")
+VA_STATIC_SCRATCH_BYTES = 32 << 20
 
 
 class Tensor4(C.Structure):
@@ -81,6 +82,7 @@ def lib() -> C.CDLL:
     handle.va_block_tables.argtypes = [C.c_int32] * 5 + [C.c_void_p, C.c_void_p, C.c_void_p]
     handle.va_prefill_workspace_bytes.argtypes = [C.POINTER(PrefillArgs), C.POINTER(C.c_size_t)]
     handle.va_prefill.argtypes = [C.POINTER(PrefillArgs), C.c_void_p]
+    handle.va_prefill_static.argtypes = [C.POINTER(PrefillArgs), C.c_void_p]
     for name in EXPORTS:
         getattr(handle, name).restype = C.c_int
     handle.va_status_string.argtypes = [C.c_int]

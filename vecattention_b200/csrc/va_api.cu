@@ -90,6 +90,7 @@ const char* va_status_string(int code) {
     case VA_ERR_ALIGN: return "pointers and strides must be multiples of 16 bytes";
     case VA_ERR_CAPACITY: return "index capacity or workspace too small";
     case VA_ERR_CUDA: return "CUDA launch failed";
+    case VA_ERR_STATIC_SCRATCH: return "problem needs more scratch than the built-in VA_STATIC_SCRATCH_BYTES array of va_prefill_static holds (use a smaller chunk_size, or va_prefill with a workspace)";
     case VA_ERR_PARAM: return "parameters rejected (q_pooling_size must be 64 or 128, chunk_size a multiple of it, causal needs q_pooling_size % k_local_size == 0 and Sq == Sk)";
     default: return "unknown status";
   }
@@ -222,6 +223,35 @@ int va_prefill(const va_prefill_args* a, va_stream_t stream_) {
     }
   }
   return VA_OK;
+}
+
+
+// ---- the operator for callers that cannot allocate device memory -----------------------------
+// The scratch of the prefill (pooled queries, per-tile counts, block tables and the selected-
+// column index lists) lives in this fixed array instead of a caller-supplied workspace.  It is
+// part of the loaded module, so every GPU that loads the library holds it until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[VA_STATIC_SCRATCH_BYTES];
+
+int va_prefill_static(const va_prefill_args* a, va_stream_t stream) {
+  if (!a) return VA_ERR_NULL;
+  PrefillPlan pl;
+  if (int rc = plan_prefill(*a, pl)) return rc;
+  if (pl.total > (size_t)VA_STATIC_SCRATCH_BYTES) return VA_ERR_STATIC_SCRATCH;
+  // In host code `g_static_scratch` names a host-side shadow of the array, not device memory: the
+  // device address must be asked for, once per device, with that device current.
+  constexpr int kMaxDevices = 64;
+  static void* scratch_of_device[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return VA_ERR_CUDA;
+  void* ptr = __atomic_load_n(&scratch_of_device[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) {
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return VA_ERR_CUDA;
+    __atomic_store_n(&scratch_of_device[dev], ptr, __ATOMIC_RELEASE);  // every thread computes the same value
+  }
+  va_prefill_args b = *a;
+  b.workspace = ptr;
+  b.workspace_bytes = VA_STATIC_SCRATCH_BYTES;
+  return va_prefill(&b, stream);
 }
 
 }  // extern "C"
