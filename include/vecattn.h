@@ -38,7 +38,9 @@ enum { VA_BF16 = 0, VA_FP16 = 1 };
 
 /* bit set in a device status word by the selection kernel when a row kept more keys than
  * the index capacity (indices beyond the capacity are dropped, the count stays exact) */
-enum { VA_STATUS_OVERFLOW = 1 };
+enum { VA_STATUS_OVERFLOW = 1,
+       /* a kernel gave up waiting on one of its internal barriers (a bug, never expected): its output is invalid */
+       VA_STATUS_TIMEOUT = 2 };
 
 typedef struct {
   const void* ptr;
@@ -106,7 +108,8 @@ int va_select(const va_select_args* args, va_stream_t stream);
  *   q, out     (B,H,Sq,D) rows q_offset .. q_offset+Sq-1 of the sequence;  k, v (B,Hkv,Sk,D)
  *   blk_count  (B,H,nq) int32, blk_idx (B,H,nq,blk_stride) int32 (may be NULL when no blocks)
  *   col_count  (B,H,nq) int32, col_idx (B,H,nq,col_stride) int32
- *   softmax_scale 0 selects 1/sqrt(D).  A tile with no key at all writes zeros. */
+ *   softmax_scale 0 selects 1/sqrt(D).  A tile with no key at all writes zeros.
+ *   Indices must satisfy 0 <= idx < Sk. */
 typedef struct {
   int32_t dtype, batch, heads, kv_heads, sq, sk, head_dim, pq;
   int32_t causal, q_offset;
@@ -119,6 +122,7 @@ typedef struct {
   const int32_t* col_idx;
   int64_t col_stride;
   float softmax_scale;
+  int32_t* status; /* optional device word receiving VA_STATUS_* bits */
 } va_attn_args;
 int va_sparse_attn(const va_attn_args* args, va_stream_t stream);
 

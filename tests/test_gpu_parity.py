@@ -206,8 +206,10 @@ def test_prefill_matches_oracle(va, cfg):
     ref, sel = O.vecattention_prefill(q, k, v, th, cfg["pq"], cfg["bk"], cfg["g"], cfg["causal"], cfg["chunk"],
                                       return_selection=True)
     th_dev = th.cuda() if isinstance(th, torch.Tensor) else th
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     out, counts = va.VecAttention_prefill(q.cuda(), k.cuda(), v.cuda(), th_dev, cfg["pq"], cfg["bk"], cfg["g"],
-                                          cfg["causal"], cfg["chunk"], return_selection=True)
+                                          cfg["causal"], cfg["chunk"], return_selection=True, status=status)
+    assert int(status.item()) == 0, "a kernel reported overflow or an internal timeout"
     ref_counts = torch.cat([c for c, _ in sel], dim=2)
     # a boundary key may flip a count by one; anything else is a bug
     assert (counts.cpu() - ref_counts).abs().sum() <= 2

@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libvecattn.so")
 
 VA_BF16, VA_FP16 = 0, 1
 VA_STATUS_OVERFLOW = 1
+VA_STATUS_TIMEOUT = 2
 
 # every symbol include/vecattn.h declares
 EXPORTS = ("va_pool_q", "va_select", "va_sparse_attn", "va_block_tables", "va_prefill_workspace_bytes",
@@ -46,7 +47,7 @@ class AttnArgs(C.Structure):
                 ("q", Tensor4), ("k", Tensor4), ("v", Tensor4), ("out", Tensor4),
                 ("blk_count", C.c_void_p), ("blk_idx", C.c_void_p), ("blk_stride", C.c_int64),
                 ("col_count", C.c_void_p), ("col_idx", C.c_void_p), ("col_stride", C.c_int64),
-                ("softmax_scale", C.c_float)]
+                ("softmax_scale", C.c_float), ("status", C.c_void_p)]
 
 
 class PrefillArgs(C.Structure):

@@ -159,7 +159,7 @@ def sparse_attn_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_poolin
 
 
 def _sparse_attn_bhsd(q, k, v, pq, block_count, block_offset, column_count, column_index, causal,
-                      q_offset=0, softmax_scale=None, out=None, out_layout="bhsd"):
+                      q_offset=0, softmax_scale=None, out=None, out_layout="bhsd", status=None):
     dev = _require_cuda(q, k, v, column_count, column_index)
     b, h, sq, d = q.shape
     hkv, sk = k.shape[1], k.shape[2]
@@ -188,7 +188,8 @@ def _sparse_attn_bhsd(q, k, v, pq, block_count, block_offset, column_count, colu
     args = L.AttnArgs(_dtype_code(q), b, h, hkv, sq, sk, d, pq, int(bool(causal)), int(q_offset),
                       _t4(q), _t4(k), _t4(v), _t4(out), bc, bo, bs,
                       column_count.data_ptr(), column_index.data_ptr(), col_stride,
-                      float(softmax_scale) if softmax_scale else 0.0)
+                      float(softmax_scale) if softmax_scale else 0.0,
+                      status.data_ptr() if status is not None else None)
     with torch.cuda.device(dev):
         _check(L.lib().va_sparse_attn(C.byref(args), _stream()))
     return out.transpose(1, 2) if out_layout == "bshd" else out
@@ -222,6 +223,7 @@ def VecAttention_prefill(
     compat_q1: bool = True,
     return_selection: bool = False,
     out: Optional[torch.Tensor] = None,
+    status: Optional[torch.Tensor] = None,
 ):
     """Vectorized sparse attention prefill (VecAttention) on B200.
 
@@ -237,6 +239,8 @@ def VecAttention_prefill(
         compat_q1: reproduce the reference's truncating-division quirk in the causal rule
         return_selection: also return the per-tile selected-column counts (B,H,nq) int32
         out: preallocated output
+        status: int32 device tensor of one element that receives VA_STATUS_* bits (index capacity
+            overflow, internal wait timeout); not cleared here, not read back here
 
     Returns:
         attn_output: (batch, num_heads, seq_len, head_dim)
@@ -273,7 +277,8 @@ def VecAttention_prefill(
                          int(bool(causal)), chunk_size, DEFAULT_COMPAT_BSQ if compat_q1 else 0,
                          _t4(q), _t4(k), _t4(v), _t4(out), gapf,
                          gaps.data_ptr() if gaps is not None else None, gstride, None, 0,
-                         counts.data_ptr() if counts is not None else None, None)
+                         counts.data_ptr() if counts is not None else None,
+                         status.data_ptr() if status is not None else None)
     nbytes = C.c_size_t(0)
     _check(L.lib().va_prefill_workspace_bytes(C.byref(args), C.byref(nbytes)))
     ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)

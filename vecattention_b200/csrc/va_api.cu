@@ -214,6 +214,7 @@ int va_prefill(const va_prefill_args* a, va_stream_t stream_) {
     aa.blk_count = bcnt; aa.blk_idx = bidx; aa.blk_stride = pl.blk_width;
     aa.col_count = cnt; aa.col_idx = idx; aa.col_stride = pl.capacity;
     aa.softmax_scale = 0.f;
+    aa.status = a->status;
     if (int rc = sparse_attn(aa, stream)) return rc;
 
     if (a->col_count_out) {

@@ -90,4 +90,17 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
   }
 }
 
+// 2^x on the special-function unit (ex2.approx: 2 ulp, 2^-inf = 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// read-only 32-bit load that the compiler keeps where it is written (used to batch index loads)
+__device__ __forceinline__ int ldg_nc(const int32_t* p) {
+  int v;
+  asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
 }  // namespace va
