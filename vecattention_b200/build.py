@@ -13,9 +13,9 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libvecattn.so")
-SOURCES = ["va_api.cu", "va_pool.cu", "va_select.cu", "va_attn.cu"]
+SOURCES = ["va_api.cu", "va_pool.cu", "va_select.cu", "va_attn.cu", "va_attn64.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC"]
+              "-Xcompiler", "-fPIC"] + os.environ.get("VA_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:

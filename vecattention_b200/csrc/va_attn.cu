@@ -19,29 +19,13 @@
 // The MMA tile is always 128 rows: with q_pooling_size 64 the upper 64 rows are zero queries.
 #include "va_common.cuh"
 #include "va_sm100.cuh"
+#include "va_attn.cuh"
 
 namespace va {
 
 using namespace sm100;
 
-struct AttnParams {
-  const void* q;
-  const void* k;
-  const void* v;
-  void* out;
-  int64_t q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh, o_ss;
-  const int32_t* blk_count;
-  const int32_t* blk_idx;
-  int64_t blk_stride;
-  const int32_t* col_count;
-  const int32_t* col_idx;
-  int64_t col_stride;
-  int32_t* status;
-  long long* dbg;
-  int heads, rep, sq, sk, nq;
-  int causal, q_offset;
-  float scale_log2;  // softmax_scale * log2(e)
-};
+int launch_attn64(const AttnParams& p, int dtype, int batch, cudaStream_t stream);  // va_attn64.cu
 
 constexpr int kChunk = 128;                // keys per step
 constexpr int kTileBytes = 128 * 256;      // one 128-row operand tile (two 16 KB halves)
@@ -49,10 +33,6 @@ constexpr int kStages = 2;
 constexpr int kAttnThreads = 288;
 constexpr size_t kAttnSmem = 1024 + (size_t)kTileBytes * (1 + 2 * kStages + 1);  // Q, K/V ring, P
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-
-#define VA_STAMP(ev, j) do { if (p.dbg && blockIdx.x == 7 && blockIdx.y == 0 && (j) < 16) p.dbg[(ev) * 16 + (j)] = clock64(); } while (0)
-static long long* g_attn_dbg = nullptr;
-extern "C" void va_debug_set_buffer(void* ptr) { g_attn_dbg = static_cast<long long*>(ptr); }
 
 struct AttnBarriers {
   uint64_t qfull, kfull[kStages], kempty[kStages], vfull[kStages], vempty[kStages];
@@ -166,7 +146,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
 #pragma unroll
         for (int i = 0; i < 16; ++i) keys_s[j & 3][(pt >> 4) + 8 * i] = keys[i];
       }
-      if (pt == 0) VA_STAMP(0, j);
 #pragma unroll
       for (int kv = 0; kv < 2; ++kv) {
         uint64_t* empty = kv ? &bars.vempty[s] : &bars.kempty[s];
@@ -184,7 +163,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
         }
         cp_async_arrive_noinc(full);
         mbar_arrive(full);
-        if (pt == 0) VA_STAMP(1 + kv, j);
       }
     }
     cp_async_commit();
@@ -202,7 +180,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
         if (!mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1)) return false;
         fence_proxy_async();
         tc_fence_after();
-        VA_STAMP(3, j);
         const uint32_t k_addr = kv_addr + (uint32_t)(s * 2) * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -220,7 +197,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
         if (!mbar_wait(&bars.pfull, j & 1)) return false;
         fence_proxy_async();
         tc_fence_after();
-        VA_STAMP(4, j);
         const uint32_t v_addr = kv_addr + (uint32_t)(s * 2 + 1) * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -254,7 +230,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
       const int* keys = keys_s[j & 3];
       if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
       tc_fence_after();
-      if (tid == 0) VA_STAMP(5, j);
       const uint32_t t_s = t_s0 + (uint32_t)sb * 128 + lane_base;
       // ---- pass 1: row maximum of the chunk ----
       float mx = -INFINITY;
@@ -277,14 +252,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
           mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
         }
       }
-      if (tid == 0) VA_STAMP(6, j);
       const float mx_s = mx * sc;
       const bool grow = mx_s > m_used + kRescaleThreshold || (m_used == -INFINITY && mx_s > -INFINITY);
       const float m_new = grow ? mx_s : m_used;
       const bool rescale = __any_sync(0xffffffffu, grow && j > 0);
       // P buffer free <=> the PV product of the previous chunk has completed, so O is quiescent
       if (!mbar_wait(&bars.pempty, (j & 1) ^ 1)) { timed_out = true; break; }
-      if (tid == 0) VA_STAMP(7, j);
       if (rescale) {
         tc_fence_after();
         const float alpha = grow ? ex2_approx(m_used - m_new) : 1.f;  // exp2(-inf) = 0 when nothing was accumulated yet
@@ -308,7 +281,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
         uint32_t v[32];
         tmem_ld32(t_s + qd * 32, v);
         tmem_wait_ld();
-        if (tid == 0) VA_STAMP(9 + qd * 3, j);
         uint32_t pk[16];
         float l0 = 0.f, l1 = 0.f;
         if (masked) {  // kept out of the arithmetic loop: a branch per element pair would serialise it
@@ -327,18 +299,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
           pk[i >> 1] = Elem<DT>::pack(p0, p1);
         }
         l += l0 + l1;
-        if (tid == 0) VA_STAMP(10 + qd * 3, j);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           *reinterpret_cast<uint4*>(p_s + tile_off(128, row, qd * 4 + c)) =
               make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
-        if (tid == 0) VA_STAMP(11 + qd * 3, j);
       }
       tc_fence_before();
       mbar_arrive(&bars.sempty[sb]);
       fence_proxy_async();
       mbar_arrive(&bars.pfull);
-      if (tid == 0) VA_STAMP(8, j);
     }
     // ---- epilogue: O / l -> global ----
     if (!timed_out && mbar_wait(&bars.ofull, 0)) {
@@ -395,15 +364,14 @@ int sparse_attn(const va_attn_args& a, cudaStream_t stream) {
   p.blk_idx = a.blk_idx; p.blk_stride = a.blk_stride;
   p.col_count = a.col_count; p.col_idx = a.col_idx; p.col_stride = a.col_stride;
   p.status = a.status;
-  p.dbg = g_attn_dbg;
   p.heads = a.heads; p.rep = a.heads / a.kv_heads; p.sq = a.sq; p.sk = a.sk;
   p.nq = (a.sq + a.pq - 1) / a.pq;
   p.causal = a.causal; p.q_offset = a.q_offset;
   const float scale = a.softmax_scale > 0.f ? a.softmax_scale : 0.08838834764831845f;
   p.scale_log2 = scale * 1.4426950408889634f;
-  if (a.dtype == VA_BF16)
-    return a.pq == 64 ? launch_attn_pq<VA_BF16, 64>(p, a.batch, stream) : launch_attn_pq<VA_BF16, 128>(p, a.batch, stream);
-  return a.pq == 64 ? launch_attn_pq<VA_FP16, 64>(p, a.batch, stream) : launch_attn_pq<VA_FP16, 128>(p, a.batch, stream);
+  if (a.pq == 64) return launch_attn64(p, a.dtype, a.batch, stream);
+  return a.dtype == VA_BF16 ? launch_attn_pq<VA_BF16, 128>(p, a.batch, stream)
+                            : launch_attn_pq<VA_FP16, 128>(p, a.batch, stream);
 }
 
 }  // namespace va

@@ -1,0 +1,436 @@
+// Vector-sparse flash attention for q_pooling_size 64 on tcgen05 weight-stationary MMAs.
+//
+// One CTA per query tile of 64 rows; keys are taken 128 at a time from the tile's dense 64-key
+// blocks and then from its selected-column list (row gather).  Both products use
+// tcgen05.mma.ws with M = 64, N = 128, whose accumulator occupies all 128 TMEM lanes: row r of
+// the 64 x 128 result lives in lane r (columns 0..63 of the result) and lane 64 + r (columns
+// 64..127), 64 TMEM columns each.  So every accumulator row is owned by two threads, each holding
+// half of it, and all four softmax warps do useful work on a 64-row tile.
+//
+// Warp roles (288 threads, one CTA per SM):
+//   warps 0-3  softmax: thread t owns half (t >> 6) of row (t & 63).  Per chunk it pulls its 64
+//              scores from tensor memory into registers (which frees the S buffer at once), forms
+//              the row maximum with its partner thread through shared memory, raises the running
+//              maximum lazily (only when a chunk exceeds it by more than 2^8), writes
+//              P = exp2(S*scale - m) in the input dtype into a double-buffered operand tile and
+//              rescales its half row of O in the rare chunks where the maximum moved.
+//   warp  4    MMA issuer (one thread): S_j = Q K_j^T, O += P_j V_j; S and P are double buffered, so
+//              the tensor pipe works on S_{j+1} and O += P_{j-1} V_{j-1} while softmax j runs.
+//   warps 5-8  gather producers: cp.async 16-byte pieces of the selected K and V rows into rings of
+//              128-byte-swizzled operand tiles (2 K stages, 3 V stages; K runs a chunk ahead of V);
+//              copy completion is reported to the stage's mbarrier asynchronously, index loads run
+//              further ahead and are exchanged inside the warp with shuffles.
+// Every wait is a bounded mbarrier wait; a timeout sets VA_STATUS_TIMEOUT and unwinds the CTA.
+#include "va_common.cuh"
+#include "va_sm100.cuh"
+#include "va_attn.cuh"
+
+namespace va {
+
+using namespace sm100;
+
+namespace {
+
+// Build with -DVA_DEBUG_STAMPS to record clock64() time stamps of one CTA's pipeline events.
+#ifdef VA_DEBUG_STAMPS
+__device__ long long g_stamps[32 * 16];
+#define VA_STAMP(ev, j) do { if (blockIdx.x == 7 && blockIdx.y == 0 && (j) < 16) g_stamps[(ev) * 16 + (j)] = clock64(); } while (0)
+#else
+#define VA_STAMP(ev, j) do { } while (0)
+#endif
+
+constexpr int kChunk = 128;
+constexpr int kKvTile = 128 * 256;  // 128 gathered rows
+constexpr int kQTile = 64 * 256;    // 64 query rows / 64 rows of P
+constexpr int kKStages = 2;  // K tiles are released as soon as S_j has been computed
+constexpr int kVStages = 3;  // V tiles live until O += P_j V_j has completed
+constexpr int kThreads = 288;
+constexpr size_t kSmem = 1024 + (size_t)kQTile * 3 + (size_t)kKvTile * (kKStages + kVStages);  // Q, P x2, K ring, V ring
+constexpr float kRescaleThreshold = 8.0f;                                            // log2 units
+
+struct Barriers {
+  uint64_t qfull, kfull[kKStages], kempty[kKStages], vfull[kVStages], vempty[kVStages];
+  uint64_t sfull[2], sempty[2], pfull[2], pempty[2], ofull, xch[2];
+};
+
+// D[tmem] (+)= A[smem] * B[smem], weight-stationary form (M = 64 uses all 128 lanes)
+__device__ __forceinline__ void umma_ws(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.ws.cta_group::1.kind::f16.collector::b0::discard [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnParams p) {
+  using T = typename Elem<DT>::T;
+  constexpr int PQ = 64;
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ Barriers bars;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int keys_s[8][kChunk];  // ring deep enough that a slot is rewritten long after its last reader
+  __shared__ float xch_s[2][128];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / p.rep;
+  const int row0 = tile * PQ;
+  const int64_t trow = ((int64_t)b * p.heads + h) * p.nq + tile;
+  const int nblk = p.blk_count ? __ldg(p.blk_count + trow) : 0;
+  const int ncol = __ldg(p.col_count + trow);
+  const int nslots = nblk * 64 + ncol;
+  const int nchunks = (nslots + kChunk - 1) / kChunk;
+  T* ob = static_cast<T*>(p.out) + b * p.o_sb + h * p.o_sh;
+
+  if (nchunks == 0) {  // no key at all: the tile's output is zero
+    for (int i = tid; i < PQ * 16; i += kThreads) {
+      const int r = i >> 4, c = i & 15;
+      if (row0 + r < p.sq) *reinterpret_cast<uint4*>(ob + (int64_t)(row0 + r) * p.o_ss + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+
+  unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+  unsigned char* q_s = smem;
+  unsigned char* p_s = smem + kQTile;       // two buffers
+  unsigned char* k_s = smem + 3 * kQTile;                          // K ring
+  unsigned char* v_s = k_s + (size_t)kKStages * kKvTile;           // V ring
+
+  if (tid == 0) {
+    mbar_init(&bars.qfull, 256);  // per producer thread: one asynchronous copy-completion arrival + one plain arrival
+    for (int s = 0; s < kKStages; ++s) {
+      mbar_init(&bars.kfull[s], 256);
+      mbar_init(&bars.kempty[s], 1);
+    }
+    for (int s = 0; s < kVStages; ++s) {
+      mbar_init(&bars.vfull[s], 256);
+      mbar_init(&bars.vempty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars.sfull[s], 1);
+      mbar_init(&bars.sempty[s], 128);
+      mbar_init(&bars.pfull[s], 128);
+      mbar_init(&bars.pempty[s], 1);
+      mbar_init(&bars.xch[s], 64);
+    }
+    mbar_init(&bars.ofull, 1);
+    fence_proxy_async();
+  }
+  if (warp == 4) {
+    tmem_alloc(&tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t t_s0 = tmem, t_o = tmem + 128;  // S buffers at columns 0 and 64, O at 128 (64 columns each)
+
+  bool timed_out = false;
+
+  if (warp >= 5) {
+    // ======================= gather producers =======================
+    const int pt = tid - 160;
+    const T* qb = static_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
+    const T* kb = static_cast<const T*>(p.k) + b * p.k_sb + hkv * p.k_sh;
+    const T* vb = static_cast<const T*>(p.v) + b * p.v_sb + hkv * p.v_sh;
+    const int32_t* blk = p.blk_idx + trow * p.blk_stride;
+    const int32_t* col = p.col_idx + trow * p.col_stride;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // Q tile: rows beyond the sequence are zero
+      const int pce = pt + i * 128, r = pce >> 4, c = pce & 15;
+      const bool ok = row0 + r < p.sq;
+      cp_async16(smem_addr(q_s + tile_off(64, r, c)), qb + (int64_t)(ok ? row0 + r : 0) * p.q_ss + c * 8, ok);
+    }
+    cp_async_arrive_noinc(&bars.qfull);
+    mbar_arrive(&bars.qfull);
+    // Copy geometry.  A warp covers two key rows per instruction: lanes 0-15 the sixteen 16-byte
+    // pieces of row rbase + 8 i, lanes 16-31 those of the next row.  Because the rows of one thread
+    // differ by multiples of 8, its swizzled piece position is the same in all of them and the
+    // shared-memory destinations are one base address plus i * 1024.
+    // Each lane fetches ONE key index per chunk (that of row rbase + 8 * (lane & 15)), one chunk
+    // ahead; the sixteen indices a thread needs are then exchanged with warp shuffles.
+    const int pw = warp - 5, hi = lane >> 4, c = lane & 15;
+    const int rbase = 2 * pw + hi;
+    const uint32_t dst_off = tile_off(128, rbase, c);
+    const int my_slot = rbase + 8 * c;
+    // The raw load is issued one chunk ahead and only interpreted at the top of the next iteration,
+    // so the (in-order) warp never stalls on the index fetch.
+    auto fetch_raw = [&](int j) -> int {
+      const int slot = j * kChunk + my_slot;
+      const int ci = min(max(slot - nblk * 64, 0), max(ncol - 1, 0));
+      return ldg_nc(slot < nblk * 64 ? blk + (slot >> 6) : col + ci);
+    };
+    auto decode = [&](int j, int raw) -> int {
+      const int slot = j * kChunk + my_slot;
+      const int key = slot < nblk * 64 ? raw + (slot & 63) : (slot < nslots ? raw : -1);
+      return (key >= 0 && key < p.sk) ? key : -1;
+    };
+    // all sixteen keys of this thread's rows, from the lanes that fetched them
+    auto spread = [&](int key, int (&out)[16]) {
+      const int kcl = max(key, 0);  // an unused slot copies row 0: its scores are masked and its P is zero
+#pragma unroll
+      for (int i = 0; i < 16; ++i) out[i] = __shfl_sync(0xffffffffu, kcl, (lane & 16) + i);
+    };
+    auto copy_tile = [&](unsigned char* tile, const T* base, int64_t stride, const int (&keys)[16], uint64_t* full) {
+      const uint32_t dst = smem_addr(tile) + dst_off;
+      const T* src = base + c * 8;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) cp_async16_full(dst + i * 1024, src + (int64_t)keys[i] * stride);
+      cp_async_arrive_noinc(full);
+      mbar_arrive(full);
+    };
+    // K runs one chunk ahead of V: K_{j+1} only needs S_{j-1} to be done, while V_j has to wait for
+    // the PV product three chunks back.  Raw index loads run one more chunk ahead and are only
+    // interpreted an iteration later, so the in-order warp never stalls on them.
+    int kcur[16], knext[16];
+    int raw1 = fetch_raw(0), raw2 = 0;
+    {
+      const int key0 = decode(0, raw1);
+      keys_s[0][my_slot] = key0;
+      spread(key0, kcur);
+      if (nchunks > 1) raw1 = fetch_raw(1);
+      if (nchunks > 2) raw2 = fetch_raw(2);
+      copy_tile(k_s, kb, p.k_ss, kcur, &bars.kfull[0]);  // K_0: the stage is free
+    }
+    for (int j = 0; j < nchunks && !timed_out; ++j) {
+      if (pt == 0) VA_STAMP(0, j);
+      if (j + 1 < nchunks) {
+        const int jn = j + 1, ks = jn % kKStages, ku = jn / kKStages;
+        const int key = decode(jn, raw1);
+        raw1 = raw2;
+        if (j + 3 < nchunks) raw2 = fetch_raw(j + 3);
+        keys_s[jn & 7][my_slot] = key;
+        spread(key, knext);
+        if (!mbar_wait(&bars.kempty[ks], (ku & 1) ^ 1)) { timed_out = true; break; }
+        if (pt == 0) VA_STAMP(1, j);
+        copy_tile(k_s + (size_t)ks * kKvTile, kb, p.k_ss, knext, &bars.kfull[ks]);
+        if (pt == 0) VA_STAMP(2, j);
+      }
+      {
+        const int vs = j % kVStages, vu = j / kVStages;
+        if (!mbar_wait(&bars.vempty[vs], (vu & 1) ^ 1)) { timed_out = true; break; }
+        if (pt == 0) VA_STAMP(3, j);
+        copy_tile(v_s + (size_t)vs * kKvTile, vb, p.v_ss, kcur, &bars.vfull[vs]);
+        if (pt == 0) VA_STAMP(4, j);
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) kcur[i] = knext[i];
+    }
+    cp_async_commit();
+    cp_async_wait<0>();  // nothing of this thread may still be in flight when the CTA retires
+  } else if (warp == 4) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
+      constexpr uint32_t idesc_s = umma_idesc(64, 128, in16, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc(64, 128, in16, 0, 1);
+      const uint32_t q_addr = smem_addr(q_s), p_addr = smem_addr(p_s), kr_addr = smem_addr(k_s), vr_addr = smem_addr(v_s);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j % kKStages, u = j / kKStages, sb = j & 1, ub = j >> 1;
+        if (!mbar_wait(&bars.kfull[s], u & 1)) return false;
+        if (!mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1)) return false;
+        fence_proxy_async();
+        tc_fence_after();
+        VA_STAMP(5, j);
+        const uint32_t k_addr = kr_addr + (uint32_t)s * kKvTile;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t qoff = (uint32_t)(ks >> 2) * (64 * 128) + (uint32_t)(ks & 3) * 32;
+          const uint32_t koff = (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32;
+          umma_ws(t_s0 + (uint32_t)sb * 64, umma_desc(q_addr + qoff, 16, 1024), umma_desc(k_addr + koff, 16, 1024),
+                  idesc_s, ks > 0);
+        }
+        umma_commit(&bars.kempty[s]);
+        umma_commit(&bars.sfull[sb]);
+        VA_STAMP(6, j);
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {
+        const int s = j % kVStages, u = j / kVStages, pb = j & 1, upb = j >> 1;
+        if (!mbar_wait(&bars.vfull[s], u & 1)) return false;
+        if (!mbar_wait(&bars.pfull[pb], upb & 1)) return false;
+        fence_proxy_async();
+        tc_fence_after();
+        VA_STAMP(7, j);
+        const uint32_t v_addr = vr_addr + (uint32_t)s * kKvTile;
+        const uint32_t pa = p_addr + (uint32_t)pb * kQTile;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t poff = (uint32_t)(ks >> 2) * (64 * 128) + (uint32_t)(ks & 3) * 32;
+          umma_ws(t_o, umma_desc(pa + poff, 16, 1024), umma_desc(v_addr + (uint32_t)ks * 16 * 128, 128 * 128, 1024),
+                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars.vempty[s]);
+        umma_commit(&bars.pempty[pb]);
+        if (j == nchunks - 1) umma_commit(&bars.ofull);
+        return true;
+      };
+      bool ok = mbar_wait(&bars.qfull, 0);
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < nchunks && ok; ++j) {
+        if (j + 1 < nchunks) ok = issue_s(j + 1);
+        if (ok) ok = issue_pv(j);
+      }
+      timed_out = !ok;
+    }
+  } else {
+    // ======================= softmax / correction / epilogue =======================
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const int row = tid & 63, half = tid >> 6, pair = warp & 1;
+    const int qpos = p.q_offset + row0 + row;
+    float m_used = -INFINITY, l = 0.f;
+    const float sc = p.scale_log2;
+    for (int j = 0; j < nchunks && !timed_out; ++j) {
+      const int sb = j & 1, ub = j >> 1;
+      const bool masked = p.causal || j == nchunks - 1 || j * kChunk < nblk * 64;
+      const int* keys = keys_s[j & 7] + half * 64;
+      if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
+      tc_fence_after();
+      if (tid == 0) VA_STAMP(8, j);
+      // ---- this thread's 64 scores -> registers; the S buffer is free again right away ----
+      uint32_t v[64];
+      {
+        uint32_t lo[32], hi[32];
+        tmem_ld32(t_s0 + (uint32_t)sb * 64 + lane_base, lo);
+        tmem_ld32(t_s0 + (uint32_t)sb * 64 + lane_base + 32, hi);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v[i] = lo[i];
+          v[32 + i] = hi[i];
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars.sempty[sb]);
+      if (masked) {  // kept out of the arithmetic loops: a branch per element would serialise them
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const int key = keys[i];
+          if (key < 0 || (p.causal && key > qpos)) v[i] = 0xff800000u;  // -inf
+        }
+      }
+      // ---- row maximum: own half, then the partner's through shared memory ----
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+      float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      xch_s[j & 1][tid] = mx;
+      mbar_arrive(&bars.xch[pair]);
+      if (!mbar_wait(&bars.xch[pair], j & 1)) { timed_out = true; break; }
+      mx = fmaxf(mx, xch_s[j & 1][tid ^ 64]);
+      if (tid == 0) VA_STAMP(9, j);
+      const float mx_s = mx * sc;
+      const bool grow = mx_s > m_used + kRescaleThreshold || (m_used == -INFINITY && mx_s > -INFINITY);
+      const float m_new = grow ? mx_s : m_used;
+      const bool rescale = __any_sync(0xffffffffu, grow && j > 0);  // same rows, hence same verdict, in the partner warp
+      // P buffer free <=> the PV product that read it two chunks ago has completed
+      if (!mbar_wait(&bars.pempty[j & 1], ((j >> 1) & 1) ^ 1)) { timed_out = true; break; }
+      if (rescale) {
+        // O must be quiescent: wait for the PV product of the previous chunk
+        if (!mbar_wait(&bars.pempty[(j - 1) & 1], ((j - 1) >> 1) & 1)) { timed_out = true; break; }
+        tc_fence_after();
+        const float alpha = grow ? ex2_approx(m_used - m_new) : 1.f;  // 2^-inf = 0 when nothing was accumulated yet
+#pragma unroll 1
+        for (int qd = 0; qd < 2; ++qd) {
+          uint32_t o[32];
+          tmem_ld32(t_o + lane_base + qd * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(t_o + lane_base + qd * 32, o);
+        }
+        tmem_wait_st();
+        l *= alpha;
+      }
+      if (tid == 0) VA_STAMP(10, j);
+      m_used = m_new;
+      const float mref = m_used == -INFINITY ? 0.f : m_used;
+      // ---- P = exp2(S * scale - m), row sum, P -> shared memory (K-major operand, this thread's 64 keys) ----
+      unsigned char* pdst = p_s + (size_t)(j & 1) * kQTile;
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + e * 2]), sc, -mref));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + e * 2 + 1]), sc, -mref));
+          l0 += p0;
+          l1 += p1;
+          pk[e] = Elem<DT>::pack(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(pdst + tile_off(64, row, half * 8 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l += l0 + l1;
+      tc_fence_before();
+      fence_proxy_async();
+      mbar_arrive(&bars.pfull[j & 1]);
+      if (tid == 0) VA_STAMP(11, j);
+    }
+    // ---- epilogue: O / l -> global; the row sum is the two halves' sums ----
+    if (!timed_out && mbar_wait(&bars.ofull, 0)) {
+      tc_fence_after();
+      xch_s[nchunks & 1][tid] = l;
+      mbar_arrive(&bars.xch[pair]);
+      if (mbar_wait(&bars.xch[pair], nchunks & 1)) {
+        l += xch_s[nchunks & 1][tid ^ 64];
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const bool row_ok = row0 + row < p.sq;
+        T* orow = ob + (int64_t)(row0 + (row_ok ? row : 0)) * p.o_ss + half * 64;
+#pragma unroll 1
+        for (int qd = 0; qd < 2; ++qd) {
+          uint32_t o[32];
+          tmem_ld32(t_o + lane_base + qd * 32, o);
+          tmem_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 w;
+              w.x = Elem<DT>::pack(__uint_as_float(o[c * 8 + 0]) * inv, __uint_as_float(o[c * 8 + 1]) * inv);
+              w.y = Elem<DT>::pack(__uint_as_float(o[c * 8 + 2]) * inv, __uint_as_float(o[c * 8 + 3]) * inv);
+              w.z = Elem<DT>::pack(__uint_as_float(o[c * 8 + 4]) * inv, __uint_as_float(o[c * 8 + 5]) * inv);
+              w.w = Elem<DT>::pack(__uint_as_float(o[c * 8 + 6]) * inv, __uint_as_float(o[c * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + qd * 32 + c * 8) = w;
+            }
+          }
+        }
+      } else {
+        timed_out = true;
+      }
+    } else {
+      timed_out = true;
+    }
+  }
+  if (timed_out && p.status) atomicOr(p.status, VA_STATUS_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem, 256);
+}
+
+template <int DT>
+int launch(const AttnParams& p, int batch, cudaStream_t stream) {
+  // per-device attribute; setting it on every launch keeps multi-device processes correct
+  if (cudaFuncSetAttribute(sparse_attn64_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) !=
+      cudaSuccess)
+    return VA_ERR_CUDA;
+  dim3 grid(p.nq, p.heads, batch);
+  sparse_attn64_kernel<DT><<<grid, kThreads, kSmem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
+}
+
+}  // namespace
+
+#ifdef VA_DEBUG_STAMPS
+extern "C" int va_debug_read_stamps(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_stamps, sizeof(long long) * 32 * 16);
+}
+#endif
+
+int launch_attn64(const AttnParams& p, int dtype, int batch, cudaStream_t stream) {
+  return dtype == VA_BF16 ? launch<VA_BF16>(p, batch, stream) : launch<VA_FP16>(p, batch, stream);
+}
+
+}  // namespace va
