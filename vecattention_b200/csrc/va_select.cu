@@ -1,19 +1,29 @@
-// Important-vector selection: pooled-Q . K^T estimate + streaming MinP threshold + compaction.
+// Important-vector selection: pooled-Q . K^T estimate + streaming MinP threshold + compaction,
+// with the estimate on tcgen05 tensor cores and the accumulator in tensor memory.
 //
 // Work decomposition.  The pooled rows of all query heads that share one KV head form one row
 // list (row R -> head hkv*rep + R/nq, tile R%nq); a CTA owns 128 consecutive rows of that list and
-// walks the keys of its KV head once, tile by tile, in ascending order.  Because one CTA sees all
-// keys of its rows in order, the running (prefix) maximum of a key-block group is a per-thread
+// walks the keys of its KV head once, 128 keys per tile, in ascending order.  Because one CTA sees
+// all keys of its rows in order, the running (prefix) maximum of a key-block group is a per-thread
 // register, every row's index list comes out ascending and deterministic, and no atomics, no
 // zero-filled buffers and no second pass are needed.
 //
-// Per key tile (BN keys): the four warps compute the 128 x BN estimate tile with mma.sync
-// (A = scaled pooled Q held in registers, B = the K tile staged in swizzled shared memory by
-// cp.async, double buffered) and park it in shared memory; then thread r walks row r of the tile
-// block by block (BK keys): block maximum -> running maximum -> keep test -> append.
+// Warp roles (288 threads, one CTA per SM):
+//   warps 5-8  producers: cp.async the next K tile (128 contiguous key rows) into a 4-stage ring of
+//              128-byte-swizzled operand tiles; completion is reported to the stage's mbarrier.
+//   warp  4    MMA issuer (one thread): S_t = Q~ K_t^T, 128 x 128 x 128 as eight tcgen05.mma, into
+//              one of two 128-column accumulator buffers in tensor memory.
+//   warps 0-3  row walkers: thread r owns pooled row r = TMEM lane r.  It reads its row of S_t
+//              32 columns at a time (the next load is in flight while the current one is walked)
+//              and per key block does: block maximum -> running maximum -> keep test
+//              fp32(s + gap) >= m -> append index.
+// All hand-offs are mbarriers with bounded waits; a timeout sets VA_STATUS_TIMEOUT.
 #include "va_common.cuh"
+#include "va_sm100.cuh"
 
 namespace va {
+
+using namespace sm100;
 
 struct SelectParams {
   const void* avg_q;  // (B,H,nq,D)
@@ -31,36 +41,104 @@ struct SelectParams {
   int causal, wo_initial, compat_bsq, tile_offset;
 };
 
-constexpr int kSelRows = 128;  // pooled rows per CTA
+namespace {
 
-template <int BK> struct SelTile { static constexpr int BN = BK < 64 ? 64 : BK; };
+// Build with -DVA_DEBUG_STAMPS to record clock64() time stamps of one CTA's pipeline events.
+#ifdef VA_DEBUG_STAMPS
+__device__ long long g_sel_stamps[16 * 16];
+#define VA_STAMP(ev, j) do { if (blockIdx.x == 1 && blockIdx.y == 0 && (j) >= 8 && (j) < 24) g_sel_stamps[(ev) * 16 + (j) - 8] = clock64(); } while (0)
+#else
+#define VA_STAMP(ev, j) do { } while (0)
+#endif
 
-template <int BK> constexpr size_t select_smem_bytes() {
-  constexpr int BN = SelTile<BK>::BN;
-  return (size_t)kSelRows * 256        // scaled pooled Q
-         + 2 * (size_t)BN * 256        // K tile, two stages
-         + (size_t)kSelRows * (BN + 1) * 4;  // estimate tile
+constexpr int kRows = 128;   // pooled rows per CTA
+constexpr int kTile = 128;   // keys per tile
+constexpr int kTileBytes = 128 * 256;
+constexpr int kStages = 4;
+constexpr int kThreads = 288;
+constexpr size_t kSmem = 1024 + (size_t)kTileBytes * (1 + kStages);
+
+struct Barriers {
+  uint64_t kfull[kStages], kempty[kStages], sfull[2], sempty[2];
+};
+
+// per-row walking state
+struct Row {
+  float run_max, gap;
+  int cnt, hi;
+  int32_t* out;
+};
+
+// keep test + append of one key without a branch:  if (fp32(s + gap) >= run_max) { base[cnt] = key; ++cnt; }
+__device__ __forceinline__ void keep_append(int32_t* base, int& cnt, float s, float gap, float run_max, int key) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .f32 t;\n\t.reg .b64 a;\n\t"
+      "add.rn.f32 t, %2, %3;\n\t"
+      "setp.ge.f32 p, t, %4;\n\t"
+      "mad.wide.s32 a, %0, 4, %1;\n\t"
+      "@p st.global.b32 [a], %5;\n\t"
+      "@p add.s32 %0, %0, 1;\n\t}"
+      : "+r"(cnt)
+      : "l"(base), "f"(s), "f"(gap), "f"(run_max), "r"(key)
+      : "memory");
+}
+
+// one key block of N (16 or 32) estimates
+template <int N>
+__device__ __forceinline__ void walk_block(const uint32_t (&v)[N], int key0, Row& row, int sk, int64_t capacity) {
+  float bmax;
+  if (key0 + N <= sk) {
+    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < N; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
+    bmax = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+  } else {  // keys past the end of the sequence (NaN padding in the reference) never count
+    bmax = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      if (key0 + j < sk) bmax = fmaxf(bmax, __uint_as_float(v[j]));
+  }
+  row.run_max = fmaxf(row.run_max, bmax);
+  if (key0 >= row.hi) return;
+  // The common case (whole block below the row's limit, room for the whole block) is straight-line
+  // code: a branch around each store would make the warp diverge N times per block.
+  const int n = row.hi - key0;
+  if (n >= N && row.cnt + N <= capacity) {
+    int cnt = row.cnt;
+#pragma unroll
+    for (int j = 0; j < N; ++j) keep_append(row.out, cnt, __uint_as_float(v[j]), row.gap, row.run_max, key0 + j);
+    row.cnt = cnt;
+  } else {
+    uint32_t mask = 0;
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      mask |= (__fadd_rn(__uint_as_float(v[j]), row.gap) >= row.run_max) ? (1u << j) : 0u;
+    if (n < N) mask &= (1u << n) - 1u;
+    while (mask) {
+      const int j = __ffs(mask) - 1;
+      mask &= mask - 1;
+      if (row.cnt < capacity) row.out[row.cnt] = key0 + j;
+      ++row.cnt;
+    }
+  }
 }
 
 template <int DT, int BK>
-__global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams p) {
   using T = typename Elem<DT>::T;
-  constexpr int BN = SelTile<BK>::BN;
-  constexpr int SS = BN + 1;  // row stride of the estimate tile (floats), odd => conflict-free row walk
-  extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* q_s = smem;
-  unsigned char* k_s = smem + kSelRows * 256;
-  float* s_s = reinterpret_cast<float*>(smem + kSelRows * 256 + 2 * BN * 256);
-  __shared__ int s_khi[4];
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ Barriers bars;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_khi;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int hkv = blockIdx.y, b = blockIdx.z;
   const int nrows = p.rep * p.nq;
-  const int row_base = blockIdx.x * kSelRows;
+  const int row_base = blockIdx.x * kRows;
 
-  // ---- per-row state (thread r owns row r of the CTA) ----
+  // ---- per-row state (threads 0..127; thread r owns row r of the CTA) ----
   const int R = row_base + tid;
-  const bool row_ok = R < nrows;
+  const bool row_ok = tid < kRows && R < nrows;
   const int h = hkv * p.rep + (row_ok ? R / p.nq : 0);
   const int tile = row_ok ? R % p.nq : 0;
   const int lo = p.wo_initial ? p.pq : 0;
@@ -72,30 +150,41 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
       const int64_t g = (int64_t)p.tile_offset + tile;
       int64_t lim = g * p.pq;
       if (p.compat_bsq > 0 && (tile % p.compat_bsq) == 0) {
-        int64_t q1 = (g - 1) * p.pq + BK;
+        const int64_t q1 = (g - 1) * p.pq + BK;
         lim = q1 < lim ? q1 : lim;
       }
       lim = lim < p.sk ? lim : p.sk;
       hi = lim > 0 ? (int)lim : 0;
     }
   }
-  const float gap = p.gaps ? __ldg(p.gaps + b * p.gaps_sb + h) : p.gap;
   const int64_t out_row = ((int64_t)b * p.heads + h) * p.nq + tile;
-  int32_t* idx_out = p.col_idx + out_row * p.capacity;
-  int cnt = 0;
-  float run_max = -INFINITY;
 
-  // CTA-wide key range [k_lo, k_hi)
-  int whi = hi;
+  if (tid == 0) s_khi = 0;
+  __syncthreads();
+  if (tid < kRows) {
+    int whi = hi;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) whi = max(whi, __shfl_xor_sync(0xffffffffu, whi, o));
-  if (lane == 0) s_khi[warp] = whi;
+    for (int o = 16; o > 0; o >>= 1) whi = max(whi, __shfl_xor_sync(0xffffffffu, whi, o));
+    if (lane == 0) atomicMax(&s_khi, whi);
+  }
+  __syncthreads();
+  const int k_hi = s_khi;                       // CTA-wide end of the key walk
+  const int t_lo = lo / kTile;
+  const int t_hi = (k_hi + kTile - 1) / kTile;  // exclusive
+  if (t_lo >= t_hi || k_hi <= lo) {             // nothing selectable for any row of this CTA
+    if (row_ok) p.col_count[out_row] = 0;
+    return;
+  }
 
-  // ---- scaled pooled Q -> shared (q~ = round(fp32(q_bar) * fp32(1/sqrt(D)))) ----
+  unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+  unsigned char* q_s = smem;
+  unsigned char* k_s = smem + kTileBytes;
+
+  // ---- scaled pooled Q -> shared operand tile (q~ = round(fp32(q_bar) * fp32(1/sqrt(D)))) ----
   {
     const float scale = 0.08838834764831845f;  // fp32(1/sqrt(128))
     const T* aq = static_cast<const T*>(p.avg_q);
-    for (int i = tid; i < kSelRows * 16; i += 128) {
+    for (int i = tid; i < kRows * 16; i += kThreads) {
       const int r = i >> 4, c = i & 15;
       const int RR = row_base + r;
       uint4 w = make_uint4(0, 0, 0, 0);
@@ -105,151 +194,208 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
         uint32_t* ww = reinterpret_cast<uint32_t*>(&w);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float2 f = Elem<DT>::unpack(ww[j]);
+          const float2 f = Elem<DT>::unpack(ww[j]);
           ww[j] = Elem<DT>::pack(__fmul_rn(f.x, scale), __fmul_rn(f.y, scale));
         }
       }
-      *reinterpret_cast<uint4*>(q_s + swz_off(r, c)) = w;
+      *reinterpret_cast<uint4*>(q_s + tile_off(128, r, c)) = w;
     }
+    fence_proxy_async();
   }
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars.kfull[s], 256);  // per producer thread: asynchronous copy-completion arrival + plain arrival
+      mbar_init(&bars.kempty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars.sfull[s], 1);
+      mbar_init(&bars.sempty[s], 128);
+    }
+    fence_proxy_async();
+  }
+  if (warp == 4) {
+    tmem_alloc(&tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
   __syncthreads();
-  const int k_hi = max(max(s_khi[0], s_khi[1]), max(s_khi[2], s_khi[3]));
-  const int t_lo = lo / BN;
-  const int t_hi = (k_hi + BN - 1) / BN;  // exclusive
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  bool timed_out = false;
 
-  // ---- A fragments: rows 32*warp .. +31, two m16 tiles, 8 k-steps ----
-  uint32_t qf[2][8][4];
+  if (warp >= 5) {
+    // ======================= K tile producers =======================
+    const int pw = warp - 5, hh = lane >> 4, c = lane & 15;
+    const int rbase = 2 * pw + hh;  // this thread copies piece c of rows rbase + 8 i, i = 0..15
+    const uint32_t dst_off = tile_off(128, rbase, c);
+    const T* kbase = static_cast<const T*>(p.k) + b * p.k_sb + hkv * p.k_sh + c * 8;
+    for (int t = t_lo; t < t_hi; ++t) {
+      const int n = t - t_lo, s = n % kStages, u = n / kStages;
+      if (!mbar_wait(&bars.kempty[s], (u & 1) ^ 1)) { timed_out = true; break; }
+      if (tid == 160) VA_STAMP(0, n);
+      const uint32_t dst = smem_addr(k_s + (size_t)s * kTileBytes) + dst_off;
+      const int key0 = t * kTile + rbase;
+      if (t * kTile + kTile <= p.sk) {
+        const T* src = kbase + (int64_t)key0 * p.k_ss;
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+        for (int i = 0; i < 16; ++i) cp_async16_full(dst + i * 1024, src + (int64_t)(8 * i) * p.k_ss);
+      } else {  // last tile: rows past the sequence re-read its last row (finite; the walker ignores them)
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      const int r = warp * 32 + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-      const int c = ks * 2 + (lane >> 4);
-      ldmatrix_x4(qf[mt][ks], smem_u32(q_s + swz_off(r, c)));
+        for (int i = 0; i < 16; ++i)
+          cp_async16_full(dst + i * 1024, kbase + (int64_t)min(key0 + 8 * i, p.sk - 1) * p.k_ss);
+      }
+      cp_async_arrive_noinc(&bars.kfull[s]);
+      mbar_arrive(&bars.kfull[s]);
+      if (tid == 160) VA_STAMP(1, n);
     }
-
-  const T* kbase = static_cast<const T*>(p.k) + b * p.k_sb + hkv * p.k_sh;
-  auto load_k_tile = [&](int t, int stage) {
-    unsigned char* dst = k_s + stage * BN * 256;
-    const int key0 = t * BN;
-#pragma unroll
-    for (int i = 0; i < BN * 16 / 128; ++i) {
-      const int pce = tid + i * 128;
-      const int r = pce >> 4, c = pce & 15;
-      const int key = key0 + r;
-      const bool ok = key < p.sk;
-      cp_async16(smem_u32(dst + swz_off(r, c)), kbase + (int64_t)(ok ? key : 0) * p.k_ss + c * 8, ok);
-    }
-  };
-
-  if (t_lo < t_hi) load_k_tile(t_lo, 0);
-  cp_async_commit();
-
-  for (int t = t_lo; t < t_hi; ++t) {
-    const int stage = (t - t_lo) & 1;
-    if (t + 1 < t_hi) load_k_tile(t + 1, stage ^ 1);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();  // K tile t visible; previous tile's row walk finished
-
-    const unsigned char* kt = k_s + stage * BN * 256;
-#pragma unroll 1
-    for (int nc = 0; nc < BN / 64; ++nc) {
-      float acc[2][8][4];
+    cp_async_wait<0>();  // nothing of this thread may still be in flight when the CTA retires
+  } else if (warp == 4) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
+      constexpr uint32_t idesc = umma_idesc(128, 128, in16, 0, 0);
+      const uint32_t q_addr = smem_addr(q_s), kr_addr = smem_addr(k_s);
+      uint64_t qd[8];
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int ks = 0; ks < 8; ++ks) qd[ks] = umma_desc(q_addr + (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32, 16, 1024);
+      for (int t = t_lo; t < t_hi; ++t) {
+        const int n = t - t_lo, s = n % kStages, u = n / kStages, sb = n & 1, ub = n >> 1;
+        if (!mbar_wait(&bars.kfull[s], u & 1) || !mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1)) { timed_out = true; break; }
+        fence_proxy_async();
+        tc_fence_after();
+        VA_STAMP(2, n);
+        const uint32_t k_addr = kr_addr + (uint32_t)s * kTileBytes;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-#pragma unroll
-        for (int np = 0; np < 4; ++np) {  // pairs of n8 tiles
-          uint32_t bf[4];
-          const int r = nc * 64 + np * 16 + (lane & 7) + (lane >> 4) * 8;
-          const int c = ks * 2 + ((lane >> 3) & 1);
-          ldmatrix_x4(bf, smem_u32(kt + swz_off(r, c)));
-#pragma unroll
-          for (int mt = 0; mt < 2; ++mt) {
-            mma16816<DT>(acc[mt][np * 2], qf[mt][ks], bf[0], bf[1]);
-            mma16816<DT>(acc[mt][np * 2 + 1], qf[mt][ks], bf[2], bf[3]);
-          }
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          umma(tmem + (uint32_t)sb * 128, qd[ks],
+               umma_desc(k_addr + (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32, 16, 1024), idesc, ks > 0);
+        umma_commit(&bars.kempty[s]);
+        umma_commit(&bars.sfull[sb]);
+        VA_STAMP(3, n);
       }
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-          const int r = warp * 32 + mt * 16 + (lane >> 2);
-          const int c = nc * 64 + nt * 8 + (lane & 3) * 2;
-          s_s[r * SS + c] = acc[mt][nt][0];
-          s_s[r * SS + c + 1] = acc[mt][nt][1];
-          s_s[(r + 8) * SS + c] = acc[mt][nt][2];
-          s_s[(r + 8) * SS + c + 1] = acc[mt][nt][3];
-        }
     }
-    __syncthreads();  // estimate tile complete
-
-    // ---- row walk: thread tid owns row tid ----
-    const float* srow = s_s + tid * SS;
-    const int key_t = t * BN;
+  } else {
+    // ======================= row walkers =======================
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    Row row;
+    row.run_max = -INFINITY;
+    row.gap = p.gaps ? __ldg(p.gaps + b * p.gaps_sb + h) : p.gap;
+    row.cnt = 0;
+    row.hi = hi;
+    row.out = p.col_idx + out_row * p.capacity;
+    int gpos = (lo / BK) % p.group_k_block;  // position of the next walked block inside its key-block group
+    const int G = p.group_k_block;
+    // one key block: group bookkeeping is uniform over the CTA, the rest is per row
+    auto block_begin = [&](int key0) -> bool {
+      if (key0 < lo || key0 >= k_hi) return false;
+      if (gpos == 0) row.run_max = -INFINITY;  // a new key-block group starts
+      gpos = gpos + 1 == G ? 0 : gpos + 1;
+      return true;
+    };
+    for (int t = t_lo; t < t_hi; ++t) {
+      const int n = t - t_lo, sb = n & 1, ub = n >> 1;
+      if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
+      tc_fence_after();
+      if (tid == 0) VA_STAMP(4, n);
+      const uint32_t t_s = tmem + (uint32_t)sb * 128 + lane_base;
+      const int key_t = t * kTile;
+      if constexpr (BK <= 32) {
+        // A rolled loop over pairs of key blocks (small code: the walkers must stay in the
+        // instruction cache); the next block's tensor-memory load is in flight while one is walked.
+        uint32_t va[BK], vb[BK];
+        auto load = [&](uint32_t (&v)[BK], int col) {
+          if constexpr (BK == 16) tmem_ld16(t_s + col, v);
+          else tmem_ld32(t_s + col, v);
+        };
+        load(va, 0);
+        tmem_wait_ld();
 #pragma unroll 1
-    for (int blk = 0; blk < BN / BK; ++blk) {
-      const int key0 = key_t + blk * BK;
-      if (key0 < lo) continue;
-      if (key0 >= k_hi) break;
-      if (((key0 / BK) % p.group_k_block) == 0) run_max = -INFINITY;  // a new key-block group starts
-      const float* sv = srow + blk * BK;
-      float bmax = -INFINITY;
-      if (key0 + BK <= p.sk) {
-#pragma unroll
-        for (int j = 0; j < BK; ++j) bmax = fmaxf(bmax, sv[j]);
+        for (int c0 = 0; c0 < kTile; c0 += 2 * BK) {
+          load(vb, c0 + BK);
+          if (block_begin(key_t + c0)) walk_block<BK>(va, key_t + c0, row, p.sk, p.capacity);
+          tmem_wait_ld();
+          if (c0 + 2 * BK < kTile) load(va, c0 + 2 * BK);
+          if (block_begin(key_t + c0 + BK)) walk_block<BK>(vb, key_t + c0 + BK, row, p.sk, p.capacity);
+          tmem_wait_ld();
+        }
       } else {
-        for (int j = 0; j < BK; ++j)
-          if (key0 + j < p.sk) bmax = fmaxf(bmax, sv[j]);
-      }
-      run_max = fmaxf(run_max, bmax);
-      if (key0 < hi) {
-        const int jn = min(BK, hi - key0);
-        for (int j = 0; j < jn; ++j) {
-          if (__fadd_rn(sv[j], gap) >= run_max) {
-            if (cnt < p.capacity) idx_out[cnt] = key0 + j;
-            ++cnt;
+        // key blocks of 64 or 128: the whole block's maximum is needed before any keep test,
+        // so the block is read twice (maximum pass, then keep pass)
+#pragma unroll 1
+        for (int kb0 = 0; kb0 < kTile; kb0 += BK) {
+          const int key0 = key_t + kb0;
+          if (!block_begin(key0)) continue;
+          float bmax = -INFINITY;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BK; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(t_s + kb0 + c0, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (key0 + c0 + j < p.sk) bmax = fmaxf(bmax, __uint_as_float(v[j]));
+          }
+          row.run_max = fmaxf(row.run_max, bmax);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BK; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(t_s + kb0 + c0, v);
+            tmem_wait_ld();
+            const int kk = key0 + c0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (kk + j < row.hi && __fadd_rn(__uint_as_float(v[j]), row.gap) >= row.run_max) {
+                if (row.cnt < p.capacity) row.out[row.cnt] = kk + j;
+                ++row.cnt;
+              }
+            }
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(&bars.sempty[sb]);
+    }
+    if (row_ok && !timed_out) {
+      p.col_count[out_row] = row.cnt;
+      if (row.cnt > p.capacity && p.status) atomicOr(p.status, VA_STATUS_OVERFLOW);
     }
   }
-  cp_async_wait<0>();
-  if (row_ok) {
-    p.col_count[out_row] = cnt;
-    if (cnt > p.capacity && p.status) atomicOr(p.status, VA_STATUS_OVERFLOW);
-  }
+  if (timed_out && p.status) atomicOr(p.status, VA_STATUS_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem, 256);
 }
 
 template <int DT, int BK>
-static int launch_select_bk(const SelectParams& p, int batch, cudaStream_t stream) {
-  constexpr size_t smem = select_smem_bytes<BK>();
+int launch_bk(const SelectParams& p, int batch, cudaStream_t stream) {
   // per-device attribute; setting it on every launch keeps multi-device processes correct
-  if (cudaFuncSetAttribute(select_kernel<DT, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  if (cudaFuncSetAttribute(select_kernel<DT, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess)
     return VA_ERR_CUDA;
   const int nrows = p.rep * p.nq;
-  dim3 grid((nrows + kSelRows - 1) / kSelRows, p.kv_heads, batch);
-  select_kernel<DT, BK><<<grid, 128, smem, stream>>>(p);
+  dim3 grid((nrows + kRows - 1) / kRows, p.kv_heads, batch);
+  select_kernel<DT, BK><<<grid, kThreads, kSmem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
 }
 
 template <int DT>
-static int launch_select_dt(const SelectParams& p, int bk, int batch, cudaStream_t stream) {
+int launch_dt(const SelectParams& p, int bk, int batch, cudaStream_t stream) {
   switch (bk) {
-    case 16: return launch_select_bk<DT, 16>(p, batch, stream);
-    case 32: return launch_select_bk<DT, 32>(p, batch, stream);
-    case 64: return launch_select_bk<DT, 64>(p, batch, stream);
-    case 128: return launch_select_bk<DT, 128>(p, batch, stream);
+    case 16: return launch_bk<DT, 16>(p, batch, stream);
+    case 32: return launch_bk<DT, 32>(p, batch, stream);
+    case 64: return launch_bk<DT, 64>(p, batch, stream);
+    case 128: return launch_bk<DT, 128>(p, batch, stream);
     default: return VA_ERR_SHAPE;
   }
 }
+
+}  // namespace
+
+#ifdef VA_DEBUG_STAMPS
+extern "C" int va_debug_read_select_stamps(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_sel_stamps, sizeof(long long) * 16 * 16);
+}
+#endif
 
 int select(const va_select_args& a, cudaStream_t stream) {
   SelectParams p;
@@ -276,8 +422,7 @@ int select(const va_select_args& a, cudaStream_t stream) {
   p.wo_initial = a.wo_initial;
   p.compat_bsq = a.compat_bsq;
   p.tile_offset = a.tile_offset;
-  return a.dtype == VA_BF16 ? launch_select_dt<VA_BF16>(p, a.bk, a.batch, stream)
-                            : launch_select_dt<VA_FP16>(p, a.bk, a.batch, stream);
+  return a.dtype == VA_BF16 ? launch_dt<VA_BF16>(p, a.bk, a.batch, stream) : launch_dt<VA_FP16>(p, a.bk, a.batch, stream);
 }
 
 }  // namespace va
