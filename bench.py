@@ -36,7 +36,9 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu
 # capture summarised under profiles/ (workload -> bytes); None until a capture exists
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"c2h8": 305.3e6}  # profiles/sparse_attn64_kernel_c2h8.md
+# the capture is of 8 heads; DRAM traffic of this kernel grows in proportion to the heads processed
+NCU_TRAFFIC_PER_HEAD_32K = 305.3e6 / 8
 D = 128
 
 
@@ -132,9 +134,10 @@ def time_cuda(fn, warmup: int, iters: int) -> float:
 def cpu_sample(name: str, threshold: float, tiles: int, sample_seed: int = 0):
     """Inputs of the bounded CPU sample: one head, the first ``tiles`` query tiles, all keys."""
     from vecattention_b200.synth import make_workload
-    wl = make_workload(name, device="cpu", heads=range(0, 1), sample_seed=sample_seed)
-    if wl.heads != 1:  # GQA: first KV group's first head
-        wl.q = wl.q[:, :1]
+    from vecattention_b200.synth import CONFIGS
+    rep = CONFIGS[name]["heads"] // CONFIGS[name]["kv_heads"]
+    wl = make_workload(name, device="cpu", heads=range(0, rep), sample_seed=sample_seed)
+    wl.q = wl.q[:, :1]  # one query head (of the first KV group)
     rows = min(wl.seq_len, tiles * wl.q_pooling_size)
     return wl, wl.q[:, :, :rows].contiguous()
 
@@ -337,9 +340,12 @@ def graft_arm(args):
         sel_bytes = (wl.q.numel() + wl.k.numel()) * esz + 4 * kept_total + 4 * counts.numel()
         peak_tf = peaks["bf16_tflops"]
         achieved_tf = flops / (att_ms * 1e-3) / 1e12
-        roofline = {"kernel": "sparse_attn_kernel", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
+        roofline = {"kernel": "sparse_attn64_kernel" if pq == 64 else "sparse_attn_kernel", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
                     "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
-                    "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "peak_source": peaks["_source"] + " burst"}
+                    "traffic": (NCU_TRAFFIC_BYTES.get(wl.name) or
+                                (NCU_TRAFFIC_PER_HEAD_32K * wl.heads if wl.name == "c2" else None)),
+                    "traffic_note": "ncu capture of 8 heads (c2h8), scaled by heads" if wl.name == "c2" else None,
+                    "peak_source": peaks["_source"] + " burst"}
         sel_gbs = sel_bytes / ((t_pool + sel_ms) * 1e-3) / 1e9
         roofline_select = {"kernel": "pool_q_kernel+select_kernel", "bound": "hbm", "achieved": sel_gbs,
                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"],
@@ -423,7 +429,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "c2h8", "mini"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--threshold", type=float, default=0.0, help="skip calibration and use this MinP threshold")
-    ap.add_argument("--cpu-tiles", type=int, default=64, help="query tiles in the bounded CPU sample")
+    ap.add_argument("--cpu-tiles", type=int, default=512, help="query tiles in the bounded CPU sample")
     ap.add_argument("--profile-window", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for `ncu --profile-from-start off`) "
                          "and skip the per-kernel, end-to-end and CPU legs")
