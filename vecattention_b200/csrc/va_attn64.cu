@@ -7,15 +7,16 @@
 // 64..127), 64 TMEM columns each.  So every accumulator row is owned by two threads, each holding
 // half of it, and all four softmax warps do useful work on a 64-row tile.
 //
-// Warp roles (288 threads, one CTA per SM):
-//   warps 0-3  softmax: thread t owns half (t >> 6) of row (t & 63).  Per chunk it pulls its 64
-//              scores from tensor memory into registers (which frees the S buffer at once), forms
-//              the row maximum with its partner thread through shared memory, raises the running
+// Warp roles (448 threads, one CTA per SM):
+//   warps 0-3, 10-13  softmax: four threads own a quarter (32 scores) of a row each.  Per chunk a
+//              thread pulls its scores from tensor memory into registers (which frees the S buffer at once), forms
+//              the row maximum with its three partner threads through shared memory, raises the running
 //              maximum lazily (only when a chunk exceeds it by more than 2^8), writes
 //              P = exp2(S*scale - m) in the input dtype into a double-buffered operand tile and
-//              rescales its half row of O in the rare chunks where the maximum moved.
-//   warp  4    MMA issuer (one thread): S_j = Q K_j^T, O += P_j V_j; S and P are double buffered, so
-//              the tensor pipe works on S_{j+1} and O += P_{j-1} V_{j-1} while softmax j runs.
+//              rescales its part of the row of O in the rare chunks where the maximum moved.
+//   warps 4,9  MMA issuers (one thread each): warp 4 issues S_j = Q K_j^T, warp 9 issues O += P_j V_j;
+//              S and P are double buffered, so the tensor pipe works on S_{j+1} and
+//              O += P_{j-1} V_{j-1} while softmax j runs.
 //   warps 5-8  gather producers: cp.async 16-byte pieces of the selected K and V rows into rings of
 //              128-byte-swizzled operand tiles (2 K stages, 3 V stages; K runs a chunk ahead of V);
 //              copy completion is reported to the stage's mbarrier asynchronously, index loads run
@@ -44,7 +45,7 @@ constexpr int kKvTile = 128 * 256;  // 128 gathered rows
 constexpr int kQTile = 64 * 256;    // 64 query rows / 64 rows of P
 constexpr int kKStages = 2;  // K tiles are released as soon as S_j has been computed
 constexpr int kVStages = 3;  // V tiles live until O += P_j V_j has completed
-constexpr int kThreads = 288;
+constexpr int kThreads = 448;
 constexpr size_t kSmem = 1024 + (size_t)kQTile * 3 + (size_t)kKvTile * (kKStages + kVStages);  // Q, P x2, K ring, V ring
 constexpr float kRescaleThreshold = 8.0f;                                            // log2 units
 
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int keys_s[8][kChunk];  // ring deep enough that a slot is rewritten long after its last reader
-  __shared__ float xch_s[2][128];
+  __shared__ float xch_s[2][256];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -110,10 +111,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars.sfull[s], 1);
-      mbar_init(&bars.sempty[s], 128);
-      mbar_init(&bars.pfull[s], 128);
+      mbar_init(&bars.sempty[s], 256);
+      mbar_init(&bars.pfull[s], 256);
       mbar_init(&bars.pempty[s], 1);
-      mbar_init(&bars.xch[s], 64);
+      mbar_init(&bars.xch[s], 128);
     }
     mbar_init(&bars.ofull, 1);
     fence_proxy_async();
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
 
   bool timed_out = false;
 
-  if (warp >= 5) {
+  if (warp >= 5 && warp <= 8) {
     // ======================= gather producers =======================
     const int pt = tid - 160;
     const T* qb = static_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
@@ -221,111 +222,108 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     }
     cp_async_commit();
     cp_async_wait<0>();  // nothing of this thread may still be in flight when the CTA retires
-  } else if (warp == 4) {
-    // ======================= MMA issuer =======================
+  } else if (warp == 4 || warp == 9) {
+    // ======================= MMA issuers =======================
+    // Two independent issuing threads, so that neither product waits behind the other's barriers:
+    // warp 4 issues S_j = Q K_j^T, warp 9 issues O += P_j V_j.
     if (lane == 0) {
       constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
-      constexpr uint32_t idesc_s = umma_idesc(64, 128, in16, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc(64, 128, in16, 0, 1);
-      const uint32_t q_addr = smem_addr(q_s), p_addr = smem_addr(p_s), kr_addr = smem_addr(k_s), vr_addr = smem_addr(v_s);
-      auto issue_s = [&](int j) -> bool {
-        const int s = j % kKStages, u = j / kKStages, sb = j & 1, ub = j >> 1;
-        if (!mbar_wait(&bars.kfull[s], u & 1)) return false;
-        if (!mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1)) return false;
-        fence_proxy_async();
-        tc_fence_after();
-        VA_STAMP(5, j);
-        const uint32_t k_addr = kr_addr + (uint32_t)s * kKvTile;
+      bool ok = true;
+      if (warp == 4) {
+        constexpr uint32_t idesc_s = umma_idesc(64, 128, in16, 0, 0);
+        const uint32_t q_addr = smem_addr(q_s), kr_addr = smem_addr(k_s);
+        ok = mbar_wait(&bars.qfull, 0);
+        for (int j = 0; j < nchunks && ok; ++j) {
+          const int s = j % kKStages, u = j / kKStages, sb = j & 1, ub = j >> 1;
+          ok = mbar_wait(&bars.kfull[s], u & 1) && mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1);
+          if (!ok) break;
+          tc_fence_after();
+          VA_STAMP(5, j);
+          const uint32_t k_addr = kr_addr + (uint32_t)s * kKvTile;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t qoff = (uint32_t)(ks >> 2) * (64 * 128) + (uint32_t)(ks & 3) * 32;
-          const uint32_t koff = (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32;
-          umma_ws(t_s0 + (uint32_t)sb * 64, umma_desc(q_addr + qoff, 16, 1024), umma_desc(k_addr + koff, 16, 1024),
-                  idesc_s, ks > 0);
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t qoff = (uint32_t)(ks >> 2) * (64 * 128) + (uint32_t)(ks & 3) * 32;
+            const uint32_t koff = (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32;
+            umma_ws(t_s0 + (uint32_t)sb * 64, umma_desc(q_addr + qoff, 16, 1024), umma_desc(k_addr + koff, 16, 1024),
+                    idesc_s, ks > 0);
+          }
+          umma_commit(&bars.kempty[s]);
+          umma_commit(&bars.sfull[sb]);
+          VA_STAMP(6, j);
         }
-        umma_commit(&bars.kempty[s]);
-        umma_commit(&bars.sfull[sb]);
-        VA_STAMP(6, j);
-        return true;
-      };
-      auto issue_pv = [&](int j) -> bool {
-        const int s = j % kVStages, u = j / kVStages, pb = j & 1, upb = j >> 1;
-        if (!mbar_wait(&bars.vfull[s], u & 1)) return false;
-        if (!mbar_wait(&bars.pfull[pb], upb & 1)) return false;
-        fence_proxy_async();
-        tc_fence_after();
-        VA_STAMP(7, j);
-        const uint32_t v_addr = vr_addr + (uint32_t)s * kKvTile;
-        const uint32_t pa = p_addr + (uint32_t)pb * kQTile;
+      } else {
+        constexpr uint32_t idesc_pv = umma_idesc(64, 128, in16, 0, 1);
+        const uint32_t p_addr = smem_addr(p_s), vr_addr = smem_addr(v_s);
+        for (int j = 0; j < nchunks && ok; ++j) {
+          const int s = j % kVStages, u = j / kVStages, pb = j & 1, upb = j >> 1;
+          ok = mbar_wait(&bars.vfull[s], u & 1) && mbar_wait(&bars.pfull[pb], upb & 1);
+          if (!ok) break;
+          tc_fence_after();
+          VA_STAMP(7, j);
+          const uint32_t v_addr = vr_addr + (uint32_t)s * kKvTile;
+          const uint32_t pa = p_addr + (uint32_t)pb * kQTile;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t poff = (uint32_t)(ks >> 2) * (64 * 128) + (uint32_t)(ks & 3) * 32;
-          umma_ws(t_o, umma_desc(pa + poff, 16, 1024), umma_desc(v_addr + (uint32_t)ks * 16 * 128, 128 * 128, 1024),
-                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t poff = (uint32_t)(ks >> 2) * (64 * 128) + (uint32_t)(ks & 3) * 32;
+            umma_ws(t_o, umma_desc(pa + poff, 16, 1024), umma_desc(v_addr + (uint32_t)ks * 16 * 128, 128 * 128, 1024),
+                    idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(&bars.vempty[s]);
+          umma_commit(&bars.pempty[pb]);
+          if (j == nchunks - 1) umma_commit(&bars.ofull);
         }
-        umma_commit(&bars.vempty[s]);
-        umma_commit(&bars.pempty[pb]);
-        if (j == nchunks - 1) umma_commit(&bars.ofull);
-        return true;
-      };
-      bool ok = mbar_wait(&bars.qfull, 0);
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < nchunks && ok; ++j) {
-        if (j + 1 < nchunks) ok = issue_s(j + 1);
-        if (ok) ok = issue_pv(j);
       }
       timed_out = !ok;
     }
   } else {
     // ======================= softmax / correction / epilogue =======================
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const int row = tid & 63, half = tid >> 6, pair = warp & 1;
+    // Eight warps.  Accumulator row r lives in TMEM lanes r and 64 + r (64 columns each); a warp can
+    // only reach the lane quarter (warp % 4), so warps 0-3 take columns 0..31 and warps 10-13 columns
+    // 32..63 of their quarter: four threads own a quarter row each and meet through shared memory.
+    const int qtr = warp & 3, colh = warp >= 10 ? 1 : 0;
+    const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
+    const int tl = qtr * 32 + lane;           // TMEM lane
+    const int row = tl & 63, half = tl >> 6;  // query row, which 64-key half of the chunk
+    const int grp = qtr & 1;                  // rows 0..31 / 32..63: the four warps that share them
+    const int member = half * 2 + colh;
     const int qpos = p.q_offset + row0 + row;
     float m_used = -INFINITY, l = 0.f;
     const float sc = p.scale_log2;
+    auto xslot = [&](int buf, int m) -> float& { return xch_s[buf][(grp * 4 + m) * 32 + lane]; };
     for (int j = 0; j < nchunks && !timed_out; ++j) {
       const int sb = j & 1, ub = j >> 1;
       const bool masked = p.causal || j == nchunks - 1 || j * kChunk < nblk * 64;
-      const int* keys = keys_s[j & 7] + half * 64;
+      const int* keys = keys_s[j & 7] + half * 64 + colh * 32;
       if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
       tc_fence_after();
       if (tid == 0) VA_STAMP(8, j);
-      // ---- this thread's 64 scores -> registers; the S buffer is free again right away ----
-      uint32_t v[64];
-      {
-        uint32_t lo[32], hi[32];
-        tmem_ld32(t_s0 + (uint32_t)sb * 64 + lane_base, lo);
-        tmem_ld32(t_s0 + (uint32_t)sb * 64 + lane_base + 32, hi);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          v[i] = lo[i];
-          v[32 + i] = hi[i];
-        }
-      }
+      // ---- this thread's 32 scores -> registers; the S buffer is free again right away ----
+      uint32_t v[32];
+      tmem_ld32(t_s0 + (uint32_t)sb * 64 + colh * 32 + lane_base, v);
+      tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&bars.sempty[sb]);
       if (masked) {  // kept out of the arithmetic loops: a branch per element would serialise them
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < 32; ++i) {
           const int key = keys[i];
           if (key < 0 || (p.causal && key > qpos)) v[i] = 0xff800000u;  // -inf
         }
       }
-      // ---- row maximum: own half, then the partner's through shared memory ----
+      // ---- row maximum: own quarter, then the three others through shared memory ----
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+      for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
       float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      xch_s[j & 1][tid] = mx;
-      mbar_arrive(&bars.xch[pair]);
-      if (!mbar_wait(&bars.xch[pair], j & 1)) { timed_out = true; break; }
-      mx = fmaxf(mx, xch_s[j & 1][tid ^ 64]);
+      xslot(j & 1, member) = mx;
+      mbar_arrive(&bars.xch[grp]);
+      if (!mbar_wait(&bars.xch[grp], j & 1)) { timed_out = true; break; }
+      mx = fmaxf(fmaxf(xslot(j & 1, 0), xslot(j & 1, 1)), fmaxf(xslot(j & 1, 2), xslot(j & 1, 3)));
       if (tid == 0) VA_STAMP(9, j);
       const float mx_s = mx * sc;
       const bool grow = mx_s > m_used + kRescaleThreshold || (m_used == -INFINITY && mx_s > -INFINITY);
       const float m_new = grow ? mx_s : m_used;
-      const bool rescale = __any_sync(0xffffffffu, grow && j > 0);  // same rows, hence same verdict, in the partner warp
+      const bool rescale = __any_sync(0xffffffffu, grow && j > 0);  // same rows, hence same verdict, in all four warps
       // P buffer free <=> the PV product that read it two chunks ago has completed
       if (!mbar_wait(&bars.pempty[j & 1], ((j >> 1) & 1) ^ 1)) { timed_out = true; break; }
       if (rescale) {
@@ -333,26 +331,23 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
         if (!mbar_wait(&bars.pempty[(j - 1) & 1], ((j - 1) >> 1) & 1)) { timed_out = true; break; }
         tc_fence_after();
         const float alpha = grow ? ex2_approx(m_used - m_new) : 1.f;  // 2^-inf = 0 when nothing was accumulated yet
-#pragma unroll 1
-        for (int qd = 0; qd < 2; ++qd) {
-          uint32_t o[32];
-          tmem_ld32(t_o + lane_base + qd * 32, o);
-          tmem_wait_ld();
+        uint32_t o[32];
+        tmem_ld32(t_o + lane_base + colh * 32, o);
+        tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(t_o + lane_base + qd * 32, o);
-        }
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st32(t_o + lane_base + colh * 32, o);
         tmem_wait_st();
         l *= alpha;
       }
       if (tid == 0) VA_STAMP(10, j);
       m_used = m_new;
       const float mref = m_used == -INFINITY ? 0.f : m_used;
-      // ---- P = exp2(S * scale - m), row sum, P -> shared memory (K-major operand, this thread's 64 keys) ----
+      // ---- P = exp2(S * scale - m), row sum, P -> shared memory (K-major operand, this thread's 32 keys) ----
       unsigned char* pdst = p_s + (size_t)(j & 1) * kQTile;
       float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t pk[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -362,7 +357,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
           l1 += p1;
           pk[e] = Elem<DT>::pack(p0, p1);
         }
-        *reinterpret_cast<uint4*>(pdst + tile_off(64, row, half * 8 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(pdst + tile_off(64, row, half * 8 + colh * 4 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       l += l0 + l1;
       tc_fence_before();
@@ -370,31 +365,28 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       mbar_arrive(&bars.pfull[j & 1]);
       if (tid == 0) VA_STAMP(11, j);
     }
-    // ---- epilogue: O / l -> global; the row sum is the two halves' sums ----
+    // ---- epilogue: O / l -> global; the row sum is the sum of the four owners' sums ----
     if (!timed_out && mbar_wait(&bars.ofull, 0)) {
       tc_fence_after();
-      xch_s[nchunks & 1][tid] = l;
-      mbar_arrive(&bars.xch[pair]);
-      if (mbar_wait(&bars.xch[pair], nchunks & 1)) {
-        l += xch_s[nchunks & 1][tid ^ 64];
+      xslot(nchunks & 1, member) = l;
+      mbar_arrive(&bars.xch[grp]);
+      if (mbar_wait(&bars.xch[grp], nchunks & 1)) {
+        l = (xslot(nchunks & 1, 0) + xslot(nchunks & 1, 1)) + (xslot(nchunks & 1, 2) + xslot(nchunks & 1, 3));
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const bool row_ok = row0 + row < p.sq;
-        T* orow = ob + (int64_t)(row0 + (row_ok ? row : 0)) * p.o_ss + half * 64;
-#pragma unroll 1
-        for (int qd = 0; qd < 2; ++qd) {
-          uint32_t o[32];
-          tmem_ld32(t_o + lane_base + qd * 32, o);
-          tmem_wait_ld();
-          if (row_ok) {
+        T* orow = ob + (int64_t)(row0 + (row_ok ? row : 0)) * p.o_ss + half * 64 + colh * 32;
+        uint32_t o[32];
+        tmem_ld32(t_o + lane_base + colh * 32, o);
+        tmem_wait_ld();
+        if (row_ok) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint4 w;
-              w.x = Elem<DT>::pack(__uint_as_float(o[c * 8 + 0]) * inv, __uint_as_float(o[c * 8 + 1]) * inv);
-              w.y = Elem<DT>::pack(__uint_as_float(o[c * 8 + 2]) * inv, __uint_as_float(o[c * 8 + 3]) * inv);
-              w.z = Elem<DT>::pack(__uint_as_float(o[c * 8 + 4]) * inv, __uint_as_float(o[c * 8 + 5]) * inv);
-              w.w = Elem<DT>::pack(__uint_as_float(o[c * 8 + 6]) * inv, __uint_as_float(o[c * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + qd * 32 + c * 8) = w;
-            }
+          for (int c = 0; c < 4; ++c) {
+            uint4 w;
+            w.x = Elem<DT>::pack(__uint_as_float(o[c * 8 + 0]) * inv, __uint_as_float(o[c * 8 + 1]) * inv);
+            w.y = Elem<DT>::pack(__uint_as_float(o[c * 8 + 2]) * inv, __uint_as_float(o[c * 8 + 3]) * inv);
+            w.z = Elem<DT>::pack(__uint_as_float(o[c * 8 + 4]) * inv, __uint_as_float(o[c * 8 + 5]) * inv);
+            w.w = Elem<DT>::pack(__uint_as_float(o[c * 8 + 6]) * inv, __uint_as_float(o[c * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 8) = w;
           }
         }
       } else {

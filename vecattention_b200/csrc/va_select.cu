@@ -8,15 +8,19 @@
 // register, every row's index list comes out ascending and deterministic, and no atomics, no
 // zero-filled buffers and no second pass are needed.
 //
-// Warp roles (288 threads, one CTA per SM):
+// Warp roles (448 threads, one CTA per SM):
 //   warps 5-8  producers: cp.async the next K tile (128 contiguous key rows) into a 4-stage ring of
 //              128-byte-swizzled operand tiles; completion is reported to the stage's mbarrier.
 //   warp  4    MMA issuer (one thread): S_t = Q~ K_t^T, 128 x 128 x 128 as eight tcgen05.mma, into
 //              one of two 128-column accumulator buffers in tensor memory.
-//   warps 0-3  row walkers: thread r owns pooled row r = TMEM lane r.  It reads its row of S_t
-//              32 columns at a time (the next load is in flight while the current one is walked)
-//              and per key block does: block maximum -> running maximum -> keep test
-//              fp32(s + gap) >= m -> append index.
+//   warps 0-3, 10-13  row walkers: pooled row r = TMEM lane r is owned by two threads, one for
+//              columns 0..63 of the tile (warps 0-3) and one for columns 64..127 (warps 10-13; a warp
+//              reaches the lane quarter warp % 4).  Per tile each pulls its 64 estimates into
+//              registers (freeing the accumulator at once) and forms its key blocks' maxima; the pair
+//              swaps them through shared memory, so both know the running maximum entering every
+//              block; each builds the keep mask fp32(s + gap) >= m of its half, they swap counts, and
+//              each appends its kept keys at its own offset of the row's list.
+//              (k_local_size 128: one block spans the whole tile; warps 0-3 walk it alone.)
 // All hand-offs are mbarriers with bounded waits; a timeout sets VA_STATUS_TIMEOUT.
 #include "va_common.cuh"
 #include "va_sm100.cuh"
@@ -55,11 +59,11 @@ constexpr int kRows = 128;   // pooled rows per CTA
 constexpr int kTile = 128;   // keys per tile
 constexpr int kTileBytes = 128 * 256;
 constexpr int kStages = 4;
-constexpr int kThreads = 288;
+constexpr int kThreads = 448;
 constexpr size_t kSmem = 1024 + (size_t)kTileBytes * (1 + kStages);
 
 struct Barriers {
-  uint64_t kfull[kStages], kempty[kStages], sfull[2], sempty[2];
+  uint64_t kfull[kStages], kempty[kStages], sfull[2], sempty[2], pair[4];
 };
 
 // per-row walking state
@@ -69,58 +73,14 @@ struct Row {
   int32_t* out;
 };
 
-// keep test + append of one key without a branch:  if (fp32(s + gap) >= run_max) { base[cnt] = key; ++cnt; }
-__device__ __forceinline__ void keep_append(int32_t* base, int& cnt, float s, float gap, float run_max, int key) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .f32 t;\n\t.reg .b64 a;\n\t"
-      "add.rn.f32 t, %2, %3;\n\t"
-      "setp.ge.f32 p, t, %4;\n\t"
-      "mad.wide.s32 a, %0, 4, %1;\n\t"
-      "@p st.global.b32 [a], %5;\n\t"
-      "@p add.s32 %0, %0, 1;\n\t}"
-      : "+r"(cnt)
-      : "l"(base), "f"(s), "f"(gap), "f"(run_max), "r"(key)
-      : "memory");
-}
-
-// one key block of N (16 or 32) estimates
-template <int N>
-__device__ __forceinline__ void walk_block(const uint32_t (&v)[N], int key0, Row& row, int sk, int64_t capacity) {
-  float bmax;
-  if (key0 + N <= sk) {
-    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int j = 0; j < N; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
-    bmax = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-  } else {  // keys past the end of the sequence (NaN padding in the reference) never count
-    bmax = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < N; ++j)
-      if (key0 + j < sk) bmax = fmaxf(bmax, __uint_as_float(v[j]));
-  }
-  row.run_max = fmaxf(row.run_max, bmax);
-  if (key0 >= row.hi) return;
-  // The common case (whole block below the row's limit, room for the whole block) is straight-line
-  // code: a branch around each store would make the warp diverge N times per block.
-  const int n = row.hi - key0;
-  if (n >= N && row.cnt + N <= capacity) {
-    int cnt = row.cnt;
-#pragma unroll
-    for (int j = 0; j < N; ++j) keep_append(row.out, cnt, __uint_as_float(v[j]), row.gap, row.run_max, key0 + j);
-    row.cnt = cnt;
-  } else {
-    uint32_t mask = 0;
-#pragma unroll
-    for (int j = 0; j < N; ++j)
-      mask |= (__fadd_rn(__uint_as_float(v[j]), row.gap) >= row.run_max) ? (1u << j) : 0u;
-    if (n < N) mask &= (1u << n) - 1u;
-    while (mask) {
-      const int j = __ffs(mask) - 1;
-      mask &= mask - 1;
-      if (row.cnt < capacity) row.out[row.cnt] = key0 + j;
-      ++row.cnt;
-    }
-  }
+// mask |= bit  where  fp32(s + gap) >= run_max   (no branch)
+__device__ __forceinline__ void keep_bit(uint32_t& mask, float s, float gap, float run_max, uint32_t bit) {
+  asm("{\n\t.reg .pred p;\n\t.reg .f32 t;\n\t"
+      "add.rn.f32 t, %1, %2;\n\t"
+      "setp.ge.f32 p, t, %3;\n\t"
+      "@p or.b32 %0, %0, %4;\n\t}"
+      : "+r"(mask)
+      : "f"(s), "f"(gap), "f"(run_max), "r"(bit));
 }
 
 template <int DT, int BK>
@@ -130,15 +90,19 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_khi;
+  __shared__ float xmax_s[4 * 2 * 4 * 32];  // [lane quarter][tile half][block][lane]: block maxima swapped by a row's two threads
+  __shared__ int xcnt_s[4 * 2 * 32];         // kept-key counts swapped by a row's two threads
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int hkv = blockIdx.y, b = blockIdx.z;
   const int nrows = p.rep * p.nq;
   const int row_base = blockIdx.x * kRows;
 
-  // ---- per-row state (threads 0..127; thread r owns row r of the CTA) ----
-  const int R = row_base + tid;
-  const bool row_ok = tid < kRows && R < nrows;
+  // ---- per-row state: walker threads (warps 0-3 and 10-13) own row (warp % 4) * 32 + lane ----
+  const bool is_walker = warp < 4 || warp >= 10;
+  const int wrow = (warp & 3) * 32 + lane;
+  const int R = row_base + wrow;
+  const bool row_ok = is_walker && R < nrows;
   const int h = hkv * p.rep + (row_ok ? R / p.nq : 0);
   const int tile = row_ok ? R % p.nq : 0;
   const int lo = p.wo_initial ? p.pq : 0;
@@ -161,7 +125,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
 
   if (tid == 0) s_khi = 0;
   __syncthreads();
-  if (tid < kRows) {
+  if (warp < 4) {
     int whi = hi;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) whi = max(whi, __shfl_xor_sync(0xffffffffu, whi, o));
@@ -209,8 +173,9 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars.sfull[s], 1);
-      mbar_init(&bars.sempty[s], 128);
+      mbar_init(&bars.sempty[s], BK <= 64 ? 256 : 128);
     }
+    for (int s = 0; s < 4; ++s) mbar_init(&bars.pair[s], 64);
     fence_proxy_async();
   }
   if (warp == 4) {
@@ -223,7 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   const uint32_t tmem = tmem_base_s;
   bool timed_out = false;
 
-  if (warp >= 5) {
+  if (warp >= 5 && warp <= 8) {
     // ======================= K tile producers =======================
     const int pw = warp - 5, hh = lane >> 4, c = lane & 15;
     const int rbase = 2 * pw + hh;  // this thread copies piece c of rows rbase + 8 i, i = 0..15
@@ -250,9 +215,9 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
     }
     cp_async_commit();
     cp_async_wait<0>();  // nothing of this thread may still be in flight when the CTA retires
-  } else if (warp == 4) {
-    // ======================= MMA issuer =======================
-    if (lane == 0) {
+  } else if (warp == 4 || warp == 9) {
+    // ======================= MMA issuer (warp 9 is idle) =======================
+    if (lane == 0 && warp == 4) {
       constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
       constexpr uint32_t idesc = umma_idesc(128, 128, in16, 0, 0);
       const uint32_t q_addr = smem_addr(q_s), kr_addr = smem_addr(k_s);
@@ -277,7 +242,8 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
     }
   } else {
     // ======================= row walkers =======================
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const int qtr = warp & 3, colh = warp >= 10 ? 1 : 0;
+    const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
     Row row;
     row.run_max = -INFINITY;
     row.gap = p.gaps ? __ldg(p.gaps + b * p.gaps_sb + h) : p.gap;
@@ -293,44 +259,121 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
       gpos = gpos + 1 == G ? 0 : gpos + 1;
       return true;
     };
-    for (int t = t_lo; t < t_hi; ++t) {
-      const int n = t - t_lo, sb = n & 1, ub = n >> 1;
-      if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
-      tc_fence_after();
-      if (tid == 0) VA_STAMP(4, n);
-      const uint32_t t_s = tmem + (uint32_t)sb * 128 + lane_base;
-      const int key_t = t * kTile;
-      if constexpr (BK <= 32) {
-        // A rolled loop over pairs of key blocks (small code: the walkers must stay in the
-        // instruction cache); the next block's tensor-memory load is in flight while one is walked.
-        uint32_t va[BK], vb[BK];
-        auto load = [&](uint32_t (&v)[BK], int col) {
-          if constexpr (BK == 16) tmem_ld16(t_s + col, v);
-          else tmem_ld32(t_s + col, v);
-        };
-        load(va, 0);
-        tmem_wait_ld();
-#pragma unroll 1
-        for (int c0 = 0; c0 < kTile; c0 += 2 * BK) {
-          load(vb, c0 + BK);
-          if (block_begin(key_t + c0)) walk_block<BK>(va, key_t + c0, row, p.sk, p.capacity);
+    if constexpr (BK <= 64) {
+      constexpr int NB = 64 / BK;  // key blocks per half tile
+      for (int t = t_lo; t < t_hi; ++t) {
+        const int n = t - t_lo, sb = n & 1, ub = n >> 1;
+        if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
+        tc_fence_after();
+        if (tid == 0) VA_STAMP(4, n);
+        const int key_t = t * kTile, key_h = key_t + colh * 64;
+        // ---- my 64 estimates -> registers; the accumulator buffer is free again ----
+        uint32_t v[64];
+        {
+          uint32_t a[32], c[32];
+          const uint32_t t_s = tmem + (uint32_t)sb * 128 + lane_base + colh * 64;
+          tmem_ld32(t_s, a);
+          tmem_ld32(t_s + 32, c);
           tmem_wait_ld();
-          if (c0 + 2 * BK < kTile) load(va, c0 + 2 * BK);
-          if (block_begin(key_t + c0 + BK)) walk_block<BK>(vb, key_t + c0 + BK, row, p.sk, p.capacity);
-          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v[i] = a[i];
+            v[32 + i] = c[i];
+          }
         }
-      } else {
-        // key blocks of 64 or 128: the whole block's maximum is needed before any keep test,
-        // so the block is read twice (maximum pass, then keep pass)
-#pragma unroll 1
-        for (int kb0 = 0; kb0 < kTile; kb0 += BK) {
-          const int key0 = key_t + kb0;
-          if (!block_begin(key0)) continue;
+        tc_fence_before();
+        mbar_arrive(&bars.sempty[sb]);
+        // ---- maxima of my key blocks (keys past the sequence end never count) ----
+        float bm[NB];
+        if (key_h + 64 <= p.sk) {
+#pragma unroll
+          for (int kb = 0; kb < NB; ++kb) {
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < BK; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[kb * BK + j]));
+            bm[kb] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+          }
+        } else {
+#pragma unroll
+          for (int kb = 0; kb < NB; ++kb) {
+            bm[kb] = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < BK; ++j)
+              if (key_h + kb * BK + j < p.sk) bm[kb] = fmaxf(bm[kb], __uint_as_float(v[kb * BK + j]));
+          }
+        }
+#pragma unroll
+        for (int kb = 0; kb < NB; ++kb) xmax_s[((qtr * 2 + colh) * 4 + kb) * 32 + lane] = bm[kb];
+        mbar_arrive(&bars.pair[qtr]);
+        if (!mbar_wait(&bars.pair[qtr], 0)) { timed_out = true; break; }
+        // ---- running maximum entering / after every block of the tile, identical in both threads ----
+        float rm_own[NB];
+        bool on_own[NB];
+#pragma unroll
+        for (int k = 0; k < 2 * NB; ++k) {
+          const bool mine = (k / NB) == colh;
+          const float m = mine ? bm[k % NB] : xmax_s[((qtr * 2 + (k / NB)) * 4 + (k % NB)) * 32 + lane];
+          const bool on = block_begin(key_t + k * BK);
+          if (on) row.run_max = fmaxf(row.run_max, m);
+          if (mine) {
+            rm_own[k % NB] = row.run_max;
+            on_own[k % NB] = on;
+          }
+        }
+        // ---- keep mask of my 64 keys ----
+        uint32_t mlo[2] = {0u, 0u}, mhi[2] = {0u, 0u};
+#pragma unroll
+        for (int kb = 0; kb < NB; ++kb) {
+          if (on_own[kb]) {
+#pragma unroll
+            for (int j = 0; j < BK; ++j) {
+              const int c = kb * BK + j;
+              if (c < 32) keep_bit(mlo[c & 1], __uint_as_float(v[c]), row.gap, rm_own[kb], 1u << c);
+              else keep_bit(mhi[c & 1], __uint_as_float(v[c]), row.gap, rm_own[kb], 1u << (c - 32));
+            }
+          }
+        }
+        unsigned long long mask = ((unsigned long long)(mhi[0] | mhi[1]) << 32) | (unsigned long long)(mlo[0] | mlo[1]);
+        const int room = row.hi - key_h;  // keys at or past the row's limit are cut off
+        if (room < 64) mask = room <= 0 ? 0ull : (mask & ((1ull << room) - 1ull));
+        const int c_own = __popcll(mask);
+        xcnt_s[(qtr * 2 + colh) * 32 + lane] = c_own;
+        mbar_arrive(&bars.pair[qtr]);
+        if (!mbar_wait(&bars.pair[qtr], 1)) { timed_out = true; break; }
+        const int c_other = xcnt_s[(qtr * 2 + (colh ^ 1)) * 32 + lane];
+        int pos = row.cnt + (colh ? c_other : 0);
+        row.cnt += c_own + c_other;
+        // ---- append my kept keys at my offset of the row's list ----
+        if (row.cnt <= p.capacity) {
+          while (mask) {
+            const int j = __ffsll((long long)mask) - 1;
+            mask &= mask - 1ull;
+            row.out[pos++] = key_h + j;
+          }
+        } else {
+          while (mask) {
+            const int j = __ffsll((long long)mask) - 1;
+            mask &= mask - 1ull;
+            if (pos < p.capacity) row.out[pos] = key_h + j;
+            ++pos;
+          }
+        }
+      }
+    } else if (colh == 0) {
+      // k_local_size 128: the block is the whole tile and its maximum is needed before any keep
+      // test, so the tile is read twice (maximum pass, then keep pass) by one thread per row
+      for (int t = t_lo; t < t_hi; ++t) {
+        const int n = t - t_lo, sb = n & 1, ub = n >> 1;
+        if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
+        tc_fence_after();
+        const uint32_t t_s = tmem + (uint32_t)sb * 128 + lane_base;
+        const int key0 = t * kTile;
+        if (block_begin(key0)) {
           float bmax = -INFINITY;
 #pragma unroll 1
           for (int c0 = 0; c0 < BK; c0 += 32) {
             uint32_t v[32];
-            tmem_ld32(t_s + kb0 + c0, v);
+            tmem_ld32(t_s + c0, v);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -340,7 +383,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
 #pragma unroll 1
           for (int c0 = 0; c0 < BK; c0 += 32) {
             uint32_t v[32];
-            tmem_ld32(t_s + kb0 + c0, v);
+            tmem_ld32(t_s + c0, v);
             tmem_wait_ld();
             const int kk = key0 + c0;
 #pragma unroll
@@ -352,11 +395,11 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
             }
           }
         }
+        tc_fence_before();
+        mbar_arrive(&bars.sempty[sb]);
       }
-      tc_fence_before();
-      mbar_arrive(&bars.sempty[sb]);
     }
-    if (row_ok && !timed_out) {
+    if (row_ok && !timed_out && colh == 0) {  // the row's count is written by the thread of the first half
       p.col_count[out_row] = row.cnt;
       if (row.cnt > p.capacity && p.status) atomicOr(p.status, VA_STATUS_OVERFLOW);
     }
