@@ -301,7 +301,8 @@ def graft_arm(args):
         flops_all = flops
     ms_step = ms_total / args.steps
     value = flops_all / (ms_step * 1e-3) / 1e12
-    n_chunks = math.ceil(wl.seq_len / chunk)
+    idx_all_bytes = wl.batch * wl.heads * wl.nq * ((wl.seq_len + 3) // 4 * 4) * 4
+    n_chunks = 1 if idx_all_bytes <= (32 << 30) else math.ceil(wl.seq_len / chunk)
     launches = args.steps * n_chunks * 4  # pool + select + block tables + attention per chunk
 
     line = None
@@ -318,17 +319,21 @@ def graft_arm(args):
         stage = {"pool_ms": t_pool}
         nqc = math.ceil(min(chunk, wl.seq_len) / pq)
         sel_ms, att_ms = 0.0, 0.0
-        for i in range(0, wl.seq_len, chunk):
-            t0, t1 = i // pq, min(wl.nq, (i + chunk) // pq)
+        # stages are timed the way the operator runs them: one launch for the whole sequence when its
+        # index lists fit the single-pass budget, else chunk by chunk
+        idx_all = wl.batch * wl.heads * wl.nq * ((wl.seq_len + 3) // 4 * 4) * 4
+        step_rows = wl.seq_len if idx_all <= (32 << 30) else chunk
+        for i in range(0, wl.seq_len, step_rows):
+            t0, t1 = i // pq, min(wl.nq, -(-(i + step_rows) // pq))
             avg_c = avg[:, :, t0:t1].contiguous()
             gap = -math.log(thr + 1e-9)
             sel = lambda: va.fuse_qk_softmax_minp_wo_causal(avg_c, wl.k, t0, gap, wl.causal, pq, bk,
                                                             wo_initial=wl.causal, group_k_block=g, trim=False)
             cc, ci = sel()
             sel_ms += time_cuda(sel, 2, 5)
-            sk_eff = min(wl.seq_len, i + chunk) if wl.causal else wl.seq_len
-            qc = wl.q[:, :, i:i + chunk]
-            oc = out[:, :, i:i + chunk]
+            sk_eff = min(wl.seq_len, i + step_rows) if wl.causal else wl.seq_len
+            qc = wl.q[:, :, i:i + step_rows]
+            oc = out[:, :, i:i + step_rows]
             bc, bi = bcnt[:, :, t0:t1].contiguous(), bidx[:, :, t0:t1].contiguous()
             att = lambda: api._sparse_attn_bhsd(qc, wl.k[:, :, :sk_eff], wl.v[:, :, :sk_eff], pq, bc, bi, cc, ci,
                                                 wl.causal, q_offset=i, out=oc)

@@ -95,6 +95,8 @@ typedef struct {
   int32_t* col_idx;
   int64_t capacity;
   int32_t* status;
+  int32_t chunk_tiles; /* > 0: avg_q spans several prefill chunks of chunk_tiles query tiles each and the
+                          compat_bsq rule restarts at every chunk boundary; 0: avg_q is one chunk */
 } va_select_args;
 int va_select(const va_select_args* args, va_stream_t stream);
 
@@ -138,8 +140,12 @@ int va_block_tables(int32_t batch, int32_t heads, int32_t seq_len, int32_t pq, i
  * q_pooling_size, k_local_size, group_k_block, causal, chunk_size),
  * spattn/src/VecAttention.py:10-123: pooling, selection and sparse attention for every chunk,
  * enqueued on one stream with no host synchronisation.  workspace must hold
- * va_prefill_workspace_bytes() bytes and be 256-byte aligned.  col_count_out (optional,
+ * va_prefill_workspace_bytes() bytes and be 256-byte aligned.  When the selected-column lists of the
+ * whole sequence fit in VA_SINGLE_PASS_INDEX_BYTES, all chunks are processed by one launch per stage
+ * (same results: chunk_size then only positions the reference's causal chunk-boundary effect);
+ * otherwise chunk_size bounds the workspace exactly as in the reference.  col_count_out (optional,
  * (B,H,ceil(Sq/pq)) int32) receives the per-tile selection counts. */
+#define VA_SINGLE_PASS_INDEX_BYTES (32ull << 30)
 typedef struct {
   int32_t dtype, batch, heads, kv_heads, sq, sk, head_dim;
   int32_t pq, bk, group_k_block, causal, chunk_size, compat_bsq;

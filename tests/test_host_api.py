@@ -35,7 +35,7 @@ def test_struct_layout_matches_header(lib):
     # include/vecattn.h and the ctypes mirror
     assert C.sizeof(lib.Tensor4) == 32
     assert C.sizeof(lib.PoolArgs) == 24 + 32 + 8
-    assert C.sizeof(lib.SelectArgs) == 56 + 8 + 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8
+    assert C.sizeof(lib.SelectArgs) == 56 + 8 + 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8
     assert C.sizeof(lib.AttnArgs) == 40 + 4 * 32 + 8 * 6 + 8 + 8
     assert C.sizeof(lib.PrefillArgs) == 56 + 4 * 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8
 
@@ -82,10 +82,24 @@ def test_prefill_workspace_bytes(lib):
     assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n)) == 0
     idx_bytes = 32 * 512 * 32768 * 4
     assert idx_bytes <= n.value <= idx_bytes + 8 * 2 ** 20
-    a.chunk_size = 8192                                  # a smaller chunk bounds the index workspace
+    # the whole sequence fits the single-pass budget: chunk_size does not change the workspace
+    a.chunk_size = 8192
     n2 = C.c_size_t(0)
     assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n2)) == 0
-    assert n2.value < n.value / 3.9
+    assert n2.value == n.value
+    # a sequence whose index lists exceed the budget: chunk_size bounds the workspace as in the reference
+    a.heads = a.kv_heads = 64
+    a.sq = a.sk = 262144
+    a.chunk_size = 32768
+    big = C.c_size_t(0)
+    assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(big)) == 0
+    assert 64 * 512 * 262144 * 4 <= big.value <= 64 * 512 * 262144 * 4 + 64 * 2 ** 20
+    a.chunk_size = 8192
+    small = C.c_size_t(0)
+    assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(small)) == 0
+    assert small.value < big.value / 3.9
+    a.heads = a.kv_heads = 32
+    a.sq = a.sk = 32768
     a.chunk_size = 100
     assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n2)) == -7
     a.chunk_size, a.causal, a.sk = 8192, 1, 4096

@@ -45,7 +45,9 @@ def test_static_scratch_prefill_equals_workspace_prefill_twice(built_library):
     from vecattention_b200 import _lib as L
     lib = L.lib()
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    for call, (seed, causal, s, chunk) in enumerate([(1, False, 2048, 1024), (2, True, 1200, 512)]):
+    # the third problem does not fit the built-in scratch in one pass, so it runs chunk by chunk there
+    # while the workspace entry point runs it in one pass: both must agree
+    for call, (seed, causal, s, chunk) in enumerate([(1, False, 2048, 1024), (2, True, 1200, 512), (3, True, 12288, 1024)]):
         g = torch.Generator().manual_seed(seed)
         q = torch.randn(1, 4, s, 128, generator=g).to(torch.bfloat16).cuda()
         k = torch.randn(1, 2, s, 128, generator=g).to(torch.bfloat16).cuda()
@@ -58,7 +60,8 @@ def test_static_scratch_prefill_equals_workspace_prefill_twice(built_library):
         a = _args(L, q, k, v, out_ws, causal, chunk, cnt_ws)
         need = C.c_size_t(0)
         assert lib.va_prefill_workspace_bytes(C.byref(a), C.byref(need)) == 0
-        assert need.value <= L.VA_STATIC_SCRATCH_BYTES
+        # (the third problem needs more than the built-in array when run in one pass)
+        assert (need.value <= L.VA_STATIC_SCRATCH_BYTES) == (call < 2)
         ws = torch.empty(need.value, dtype=torch.uint8, device="cuda")
         a.workspace, a.workspace_bytes = ws.data_ptr(), need.value
         assert lib.va_prefill(C.byref(a), stream) == 0

@@ -43,12 +43,12 @@ static inline bool bk_ok(int bk) { return bk == 16 || bk == 32 || bk == 64 || bk
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct PrefillPlan {
-  int nq_total, nqc_max, blk_width;
+  int nq_total, nqc_max, blk_width, step;  // step: query rows handled per launch
   int64_t capacity;
   size_t off_avg, off_cnt, off_idx, off_bcnt, off_bidx, total;
 };
 
-static int plan_prefill(const va_prefill_args& a, PrefillPlan& pl) {
+static int plan_prefill(const va_prefill_args& a, PrefillPlan& pl, size_t single_pass_budget = VA_SINGLE_PASS_INDEX_BYTES) {
   if (a.dtype != VA_BF16 && a.dtype != VA_FP16) return VA_ERR_DTYPE;
   if (a.head_dim != kHeadDim || a.batch <= 0 || a.heads <= 0 || a.kv_heads <= 0 || a.sq <= 0 || a.sk <= 0)
     return VA_ERR_SHAPE;
@@ -61,9 +61,12 @@ static int plan_prefill(const va_prefill_args& a, PrefillPlan& pl) {
   const size_t bh = (size_t)a.batch * a.heads;
   const int chunk = a.chunk_size < a.sq ? a.chunk_size : a.sq;
   pl.nq_total = (a.sq + a.pq - 1) / a.pq;
-  pl.nqc_max = (chunk + a.pq - 1) / a.pq;
   pl.blk_width = a.causal ? 2 * (a.pq / 64) : 1;
   pl.capacity = (a.sk + 3) / 4 * 4;
+  // one launch per stage for the whole sequence when its index lists fit the budget
+  const bool single = bh * (size_t)pl.nq_total * (size_t)pl.capacity * 4 <= single_pass_budget;
+  pl.step = single ? a.sq : chunk;
+  pl.nqc_max = (pl.step + a.pq - 1) / a.pq;
   size_t off = 0;
   pl.off_avg = off;  off = align_up(off + bh * pl.nqc_max * kHeadDim * 2, 256);
   pl.off_cnt = off;  off = align_up(off + bh * pl.nqc_max * 4, 256);
@@ -116,7 +119,7 @@ int va_select(const va_select_args* a, va_stream_t stream) {
   if (!bk_ok(a->bk) || a->group_k_block <= 0 || a->pq <= 0) return VA_ERR_SHAPE;
   if ((a->causal || a->wo_initial) && a->pq % a->bk != 0) return VA_ERR_PARAM;
   if (a->capacity <= 0) return VA_ERR_CAPACITY;
-  if (a->compat_bsq < 0 || a->tile_offset < 0) return VA_ERR_SHAPE;
+  if (a->compat_bsq < 0 || a->tile_offset < 0 || a->chunk_tiles < 0) return VA_ERR_SHAPE;
   if (int rc = check_tensor(a->k)) return rc;
   if (!aligned16(a->avg_q)) return VA_ERR_ALIGN;
   return select(*a, reinterpret_cast<cudaStream_t>(stream));
@@ -159,10 +162,10 @@ int va_prefill_workspace_bytes(const va_prefill_args* a, size_t* bytes) {
   return VA_OK;
 }
 
-int va_prefill(const va_prefill_args* a, va_stream_t stream_) {
+static int run_prefill(const va_prefill_args* a, size_t single_pass_budget, va_stream_t stream_) {
   if (!a || !a->workspace) return VA_ERR_NULL;
   PrefillPlan pl;
-  if (int rc = plan_prefill(*a, pl)) return rc;
+  if (int rc = plan_prefill(*a, pl, single_pass_budget)) return rc;
   if (a->workspace_bytes < pl.total) return VA_ERR_CAPACITY;
   if ((reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0) return VA_ERR_ALIGN;
   if (int rc = check_tensor(a->q)) return rc;
@@ -179,8 +182,8 @@ int va_prefill(const va_prefill_args* a, va_stream_t stream_) {
   const int bh = a->batch * a->heads;
   const size_t esz = 2;
 
-  for (int i = 0; i < a->sq; i += a->chunk_size) {  // VecAttention.py:94
-    const int sqc = (a->sq - i) < a->chunk_size ? (a->sq - i) : a->chunk_size;
+  for (int i = 0; i < a->sq; i += pl.step) {  // VecAttention.py:94 (one iteration when the whole sequence fits)
+    const int sqc = (a->sq - i) < pl.step ? (a->sq - i) : pl.step;
     const int nqc = (sqc + a->pq - 1) / a->pq;
     va_tensor4 qc = a->q;
     qc.ptr = static_cast<const unsigned char*>(a->q.ptr) + (size_t)i * a->q.stride_s * esz;
@@ -198,6 +201,7 @@ int va_prefill(const va_prefill_args* a, va_stream_t stream_) {
     sa.compat_bsq = a->compat_bsq; sa.tile_offset = i / a->pq;
     sa.avg_q = avg; sa.k = a->k; sa.gap = a->gap; sa.gaps = a->gaps; sa.gaps_stride_b = a->gaps_stride_b;
     sa.col_count = cnt; sa.col_idx = idx; sa.capacity = pl.capacity; sa.status = a->status;
+    sa.chunk_tiles = a->chunk_size / a->pq;
     if (int rc = select(sa, stream)) return rc;
 
     block_tables_kernel<<<(bh * nqc + 255) / 256, 256, 0, stream>>>(bh, a->sq, a->pq, a->causal, i / a->pq, nqc, bcnt,
@@ -207,7 +211,7 @@ int va_prefill(const va_prefill_args* a, va_stream_t stream_) {
     va_attn_args aa{};
     aa.dtype = a->dtype; aa.batch = a->batch; aa.heads = a->heads; aa.kv_heads = a->kv_heads;
     aa.sq = sqc; aa.head_dim = a->head_dim; aa.pq = a->pq;
-    const int64_t kend = (int64_t)i + a->chunk_size;
+    const int64_t kend = (int64_t)i + pl.step;
     aa.sk = a->causal ? (int)(kend < a->sk ? kend : a->sk) : a->sk;  // VecAttention.py:107-108
     aa.causal = a->causal; aa.q_offset = i;
     aa.q = qc; aa.k = a->k; aa.v = a->v; aa.out = oc;
@@ -226,6 +230,7 @@ int va_prefill(const va_prefill_args* a, va_stream_t stream_) {
   return VA_OK;
 }
 
+int va_prefill(const va_prefill_args* a, va_stream_t stream) { return run_prefill(a, VA_SINGLE_PASS_INDEX_BYTES, stream); }
 
 // ---- the operator for callers that cannot allocate device memory -----------------------------
 // The scratch of the prefill (pooled queries, per-tile counts, block tables and the selected-
@@ -235,9 +240,15 @@ static __device__ __align__(256) unsigned char g_static_scratch[VA_STATIC_SCRATC
 
 int va_prefill_static(const va_prefill_args* a, va_stream_t stream) {
   if (!a) return VA_ERR_NULL;
+  // one pass over the whole sequence if that fits the array, else chunk by chunk
+  size_t budget = VA_STATIC_SCRATCH_BYTES;
   PrefillPlan pl;
-  if (int rc = plan_prefill(*a, pl)) return rc;
-  if (pl.total > (size_t)VA_STATIC_SCRATCH_BYTES) return VA_ERR_STATIC_SCRATCH;
+  if (int rc = plan_prefill(*a, pl, budget)) return rc;
+  if (pl.total > (size_t)VA_STATIC_SCRATCH_BYTES) {
+    budget = 0;
+    if (int rc = plan_prefill(*a, pl, budget)) return rc;
+    if (pl.total > (size_t)VA_STATIC_SCRATCH_BYTES) return VA_ERR_STATIC_SCRATCH;
+  }
   // In host code `g_static_scratch` names a host-side shadow of the array, not device memory: the
   // device address must be asked for, once per device, with that device current.
   constexpr int kMaxDevices = 64;
@@ -252,7 +263,7 @@ int va_prefill_static(const va_prefill_args* a, va_stream_t stream) {
   va_prefill_args b = *a;
   b.workspace = ptr;
   b.workspace_bytes = VA_STATIC_SCRATCH_BYTES;
-  return va_prefill(&b, stream);
+  return run_prefill(&b, budget, stream);
 }
 
 }  // extern "C"

@@ -42,7 +42,7 @@ struct SelectParams {
   int32_t* status;
   int heads, kv_heads, rep, nq, sk;
   int pq, group_k_block;
-  int causal, wo_initial, compat_bsq, tile_offset;
+  int causal, wo_initial, compat_bsq, tile_offset, chunk_tiles;
 };
 
 namespace {
@@ -72,6 +72,12 @@ struct Row {
   int cnt, hi;
   int32_t* out;
 };
+
+// 4-byte global store executed only where `pred` is true, without a branch
+__device__ __forceinline__ void st_global_if(int32_t* ptr, int value, bool pred) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p st.global.b32 [%0], %1;\n\t}" ::"l"(ptr), "r"(value), "r"((int)pred)
+               : "memory");
+}
 
 // mask |= bit  where  fp32(s + gap) >= run_max   (no branch)
 __device__ __forceinline__ void keep_bit(uint32_t& mask, float s, float gap, float run_max, uint32_t bit) {
@@ -113,7 +119,8 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
     } else {
       const int64_t g = (int64_t)p.tile_offset + tile;
       int64_t lim = g * p.pq;
-      if (p.compat_bsq > 0 && (tile % p.compat_bsq) == 0) {
+      const int tile_in_chunk = p.chunk_tiles > 0 ? tile % p.chunk_tiles : tile;
+      if (p.compat_bsq > 0 && (tile_in_chunk % p.compat_bsq) == 0) {
         const int64_t q1 = (g - 1) * p.pq + BK;
         lim = q1 < lim ? q1 : lim;
       }
@@ -345,10 +352,20 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         row.cnt += c_own + c_other;
         // ---- append my kept keys at my offset of the row's list ----
         if (row.cnt <= p.capacity) {
+          // The first eight kept keys go out as straight-line predicated stores (no divergence: the
+          // lanes of a warp keep different numbers of keys), the rare rest in a loop.
+          int32_t* wp = row.out + pos;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int j = __ffsll((long long)mask) - 1;
+            st_global_if(wp + e, key_h + j, mask != 0ull);
+            mask &= mask - 1ull;
+          }
+          wp += 8;
           while (mask) {
             const int j = __ffsll((long long)mask) - 1;
             mask &= mask - 1ull;
-            row.out[pos++] = key_h + j;
+            *wp++ = key_h + j;
           }
         } else {
           while (mask) {
@@ -465,6 +482,7 @@ int select(const va_select_args& a, cudaStream_t stream) {
   p.wo_initial = a.wo_initial;
   p.compat_bsq = a.compat_bsq;
   p.tile_offset = a.tile_offset;
+  p.chunk_tiles = a.chunk_tiles;
   return a.dtype == VA_BF16 ? launch_dt<VA_BF16>(p, a.bk, a.batch, stream) : launch_dt<VA_FP16>(p, a.bk, a.batch, stream);
 }
 
