@@ -106,4 +106,7 @@ __device__ __forceinline__ int ldg_nc(const int32_t* p) {
   return v;
 }
 
+// pull the 128-byte line at `p` into L2 (no register result, no wait)
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 }  // namespace va
