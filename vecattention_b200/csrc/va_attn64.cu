@@ -8,9 +8,9 @@
 // half of it, and all four softmax warps do useful work on a 64-row tile.
 //
 // Warp roles (448 threads, one CTA per SM):
-//   warps 0-3, 10-13  softmax: four threads own a quarter (32 scores) of a row each.  Per chunk a
-//              thread pulls its scores from tensor memory into registers (which frees the S buffer at once), forms
-//              the row maximum with its three partner threads through shared memory, raises the running
+//   warps 0-3, 10-13  softmax: two groups of four warps take alternate chunks; inside a group two
+//              threads own half a row (64 scores) each.  Per chunk a thread pulls its scores from tensor memory into registers (which frees the S buffer at once), forms
+//              the row maximum with its partner thread through shared memory, raises the running
 //              maximum lazily (only when a chunk exceeds it by more than 2^8), writes
 //              P = exp2(S*scale - m) in the input dtype into a double-buffered operand tile and
 //              rescales its part of the row of O in the rare chunks where the maximum moved.
@@ -51,7 +51,7 @@ constexpr float kRescaleThreshold = 8.0f;                                       
 
 struct Barriers {
   uint64_t qfull, kfull[kKStages], kempty[kKStages], vfull[kVStages], vempty[kVStages];
-  uint64_t sfull[2], sempty[2], pfull[2], pempty[2], ofull, xch[2];
+  uint64_t sfull[2], sempty[2], pfull[2], pempty[2], ofull, xch[4], dec[2], fin;
 };
 
 // D[tmem] (+)= A[smem] * B[smem], weight-stationary form (M = 64 uses all 128 lanes)
@@ -72,7 +72,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int keys_s[8][kChunk];  // ring deep enough that a slot is rewritten long after its last reader
-  __shared__ float xch_s[2][256];
+  __shared__ float xch_s[2][256];   // [group][phase][TMEM lane]: chunk maxima swapped by a row's two owners
+  __shared__ float m_row_s[2][64];   // [chunk parity][row]: the rows' shared reference maxima (exp2 domain)
+  __shared__ float fin_s[256];       // [group][TMEM lane]: row sums, added in the epilogue
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -111,11 +113,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars.sfull[s], 1);
-      mbar_init(&bars.sempty[s], 256);
-      mbar_init(&bars.pfull[s], 256);
+      mbar_init(&bars.sempty[s], 128);
+      mbar_init(&bars.pfull[s], 128);
       mbar_init(&bars.pempty[s], 1);
-      mbar_init(&bars.xch[s], 128);
+      mbar_init(&bars.dec[s], 128);
     }
+    for (int s = 0; s < 4; ++s) mbar_init(&bars.xch[s], 64);
+    mbar_init(&bars.fin, 256);
     mbar_init(&bars.ofull, 1);
     fence_proxy_async();
   }
@@ -277,77 +281,104 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     }
   } else {
     // ======================= softmax / correction / epilogue =======================
-    // Eight warps.  Accumulator row r lives in TMEM lanes r and 64 + r (64 columns each); a warp can
-    // only reach the lane quarter (warp % 4), so warps 0-3 take columns 0..31 and warps 10-13 columns
-    // 32..63 of their quarter: four threads own a quarter row each and meet through shared memory.
-    const int qtr = warp & 3, colh = warp >= 10 ? 1 : 0;
+    // Two groups of four warps work on alternate chunks (group 0 = warps 0-3 the even ones, group 1
+    // = warps 10-13 the odd ones), so the latencies of one chunk's softmax (tensor-memory load,
+    // maximum exchange, exponentials, shared-memory stores) overlap the other's.  Inside a group,
+    // accumulator row r lives in TMEM lanes r and 64 + r (64 columns each; a warp reaches the lane
+    // quarter warp % 4): two threads own half a row each and meet through shared memory.
+    // The reference maximum of a row is one value shared by both groups (m_row_s): the decision for
+    // chunk g starts from the value left by chunk g - 1, so all P tiles and O stay on one scale.
+    const int grp = warp >= 10 ? 1 : 0;
+    const int qtr = warp & 3;
     const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
     const int tl = qtr * 32 + lane;           // TMEM lane
     const int row = tl & 63, half = tl >> 6;  // query row, which 64-key half of the chunk
-    const int grp = qtr & 1;                  // rows 0..31 / 32..63: the four warps that share them
-    const int member = half * 2 + colh;
+    const int pair = qtr & 1;                 // rows 0..31 / 32..63: the two warps of the group that share them
     const int qpos = p.q_offset + row0 + row;
-    float m_used = -INFINITY, l = 0.f;
+    float m_seen = -INFINITY, l = 0.f;        // reference this thread's row sum is currently scaled to
     const float sc = p.scale_log2;
-    auto xslot = [&](int buf, int m) -> float& { return xch_s[buf][(grp * 4 + m) * 32 + lane]; };
-    for (int j = 0; j < nchunks && !timed_out; ++j) {
-      const int sb = j & 1, ub = j >> 1;
+    float* xbuf = xch_s[grp];                 // [2 phases][128]
+    int xc = 0;
+    for (int j = grp; j < nchunks && !timed_out; j += 2) {
+      const int sb = grp, ub = j >> 1;
       const bool masked = p.causal || j == nchunks - 1 || j * kChunk < nblk * 64;
-      const int* keys = keys_s[j & 7] + half * 64 + colh * 32;
+      const int* keys = keys_s[j & 7] + half * 64;
       if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
       tc_fence_after();
       if (tid == 0) VA_STAMP(8, j);
-      // ---- this thread's 32 scores -> registers; the S buffer is free again right away ----
-      uint32_t v[32];
-      tmem_ld32(t_s0 + (uint32_t)sb * 64 + colh * 32 + lane_base, v);
-      tmem_wait_ld();
+      // ---- this thread's 64 scores -> registers; the S buffer is free again right away ----
+      uint32_t v[64];
+      {
+        uint32_t lo[32], hi[32];
+        tmem_ld32(t_s0 + (uint32_t)sb * 64 + lane_base, lo);
+        tmem_ld32(t_s0 + (uint32_t)sb * 64 + lane_base + 32, hi);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v[i] = lo[i];
+          v[32 + i] = hi[i];
+        }
+      }
       tc_fence_before();
       mbar_arrive(&bars.sempty[sb]);
       if (masked) {  // kept out of the arithmetic loops: a branch per element would serialise them
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 64; ++i) {
           const int key = keys[i];
           if (key < 0 || (p.causal && key > qpos)) v[i] = 0xff800000u;  // -inf
         }
       }
-      // ---- row maximum: own quarter, then the three others through shared memory ----
+      // ---- row maximum of the chunk: own half, then the partner's through shared memory ----
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+      for (int i = 0; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
       float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      xslot(j & 1, member) = mx;
-      mbar_arrive(&bars.xch[grp]);
-      if (!mbar_wait(&bars.xch[grp], j & 1)) { timed_out = true; break; }
-      mx = fmaxf(fmaxf(xslot(j & 1, 0), xslot(j & 1, 1)), fmaxf(xslot(j & 1, 2), xslot(j & 1, 3)));
+      xbuf[(xc & 1) * 128 + tl] = mx;
+      mbar_arrive(&bars.xch[grp * 2 + pair]);
+      if (!mbar_wait(&bars.xch[grp * 2 + pair], xc & 1)) { timed_out = true; break; }
+      mx = fmaxf(mx, xbuf[(xc & 1) * 128 + (tl ^ 64)]);
+      ++xc;
       if (tid == 0) VA_STAMP(9, j);
+      // ---- the row's reference maximum: continue from what the previous chunk (other group) left ----
+      if (j > 0 && !mbar_wait(&bars.dec[grp ^ 1], ((j - 1) >> 1) & 1)) { timed_out = true; break; }
+      const float m_prev = j > 0 ? m_row_s[(j - 1) & 1][row] : -INFINITY;
       const float mx_s = mx * sc;
-      const bool grow = mx_s > m_used + kRescaleThreshold || (m_used == -INFINITY && mx_s > -INFINITY);
-      const float m_new = grow ? mx_s : m_used;
-      const bool rescale = __any_sync(0xffffffffu, grow && j > 0);  // same rows, hence same verdict, in all four warps
+      const bool grow = mx_s > m_prev + kRescaleThreshold || (m_prev == -INFINITY && mx_s > -INFINITY);
+      const float m_new = grow ? mx_s : m_prev;
+      // Written to the slot of this chunk's parity, never to the one just read: the row's other owner
+      // (in another warp) may not have read it yet.  Both owners write the same value.
+      m_row_s[j & 1][row] = m_new;
+      mbar_arrive(&bars.dec[grp]);
+      const bool rescale = __any_sync(0xffffffffu, grow && j > 0);  // same rows, hence same verdict, in the partner warp
       // P buffer free <=> the PV product that read it two chunks ago has completed
-      if (!mbar_wait(&bars.pempty[j & 1], ((j >> 1) & 1) ^ 1)) { timed_out = true; break; }
+      if (!mbar_wait(&bars.pempty[sb], (ub & 1) ^ 1)) { timed_out = true; break; }
       if (rescale) {
         // O must be quiescent: wait for the PV product of the previous chunk
-        if (!mbar_wait(&bars.pempty[(j - 1) & 1], ((j - 1) >> 1) & 1)) { timed_out = true; break; }
+        if (!mbar_wait(&bars.pempty[sb ^ 1], ((j - 1) >> 1) & 1)) { timed_out = true; break; }
         tc_fence_after();
-        const float alpha = grow ? ex2_approx(m_used - m_new) : 1.f;  // 2^-inf = 0 when nothing was accumulated yet
-        uint32_t o[32];
-        tmem_ld32(t_o + lane_base + colh * 32, o);
-        tmem_wait_ld();
+        const float alpha = grow ? ex2_approx(m_prev - m_new) : 1.f;  // 2^-inf = 0 when nothing was accumulated yet
+#pragma unroll 1
+        for (int qd = 0; qd < 2; ++qd) {
+          uint32_t o[32];
+          tmem_ld32(t_o + lane_base + qd * 32, o);
+          tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tmem_st32(t_o + lane_base + colh * 32, o);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(t_o + lane_base + qd * 32, o);
+        }
         tmem_wait_st();
-        l *= alpha;
+      }
+      if (m_seen != m_new) {  // bring this thread's row sum to the current scale (also after the other group moved it)
+        l *= ex2_approx(m_seen - m_new);
+        m_seen = m_new;
       }
       if (tid == 0) VA_STAMP(10, j);
-      m_used = m_new;
-      const float mref = m_used == -INFINITY ? 0.f : m_used;
-      // ---- P = exp2(S * scale - m), row sum, P -> shared memory (K-major operand, this thread's 32 keys) ----
-      unsigned char* pdst = p_s + (size_t)(j & 1) * kQTile;
+      const float mref = m_new == -INFINITY ? 0.f : m_new;
+      // ---- P = exp2(S * scale - m), row sum, P -> shared memory (K-major operand, this thread's 64 keys) ----
+      unsigned char* pdst = p_s + (size_t)sb * kQTile;
       float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 8; ++c) {
         uint32_t pk[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -357,26 +388,35 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
           l1 += p1;
           pk[e] = Elem<DT>::pack(p0, p1);
         }
-        *reinterpret_cast<uint4*>(pdst + tile_off(64, row, half * 8 + colh * 4 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(pdst + tile_off(64, row, half * 8 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       l += l0 + l1;
       tc_fence_before();
       fence_proxy_async();
-      mbar_arrive(&bars.pfull[j & 1]);
+      mbar_arrive(&bars.pfull[sb]);
       if (tid == 0) VA_STAMP(11, j);
     }
-    // ---- epilogue: O / l -> global; the row sum is the sum of the four owners' sums ----
-    if (!timed_out && mbar_wait(&bars.ofull, 0)) {
+    // ---- epilogue: O / l -> global.  Every thread first brings its row sum to the final scale
+    // (the last chunk's decision), then the four owners of a row add their sums. ----
+    int jl = 0;
+    if (!timed_out) {
+      jl = nchunks - 1;  // the last chunk, decided by group (jl & 1)
+      if (!mbar_wait(&bars.dec[jl & 1], (jl >> 1) & 1) || !mbar_wait(&bars.ofull, 0)) timed_out = true;
+    }
+    if (!timed_out) {
       tc_fence_after();
-      xslot(nchunks & 1, member) = l;
-      mbar_arrive(&bars.xch[grp]);
-      if (mbar_wait(&bars.xch[grp], nchunks & 1)) {
-        l = (xslot(nchunks & 1, 0) + xslot(nchunks & 1, 1)) + (xslot(nchunks & 1, 2) + xslot(nchunks & 1, 3));
+      const float m_fin = m_row_s[jl & 1][row];
+      if (m_seen != m_fin) l *= ex2_approx(m_seen - m_fin);  // l == 0 when m_seen == -inf
+      fin_s[grp * 128 + tl] = l;
+      mbar_arrive(&bars.fin);
+      if (mbar_wait(&bars.fin, 0)) {
+        l = (fin_s[tl] + fin_s[tl ^ 64]) + (fin_s[128 + tl] + fin_s[128 + (tl ^ 64)]);
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const bool row_ok = row0 + row < p.sq;
-        T* orow = ob + (int64_t)(row0 + (row_ok ? row : 0)) * p.o_ss + half * 64 + colh * 32;
+        // the two groups split the 64 columns of a lane: group 0 writes the lower 32, group 1 the upper
+        T* orow = ob + (int64_t)(row0 + (row_ok ? row : 0)) * p.o_ss + half * 64 + grp * 32;
         uint32_t o[32];
-        tmem_ld32(t_o + lane_base + colh * 32, o);
+        tmem_ld32(t_o + lane_base + grp * 32, o);
         tmem_wait_ld();
         if (row_ok) {
 #pragma unroll
@@ -392,8 +432,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       } else {
         timed_out = true;
       }
-    } else {
-      timed_out = true;
     }
   }
   if (timed_out && p.status) atomicOr(p.status, VA_STATUS_TIMEOUT);
