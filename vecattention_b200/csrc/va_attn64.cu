@@ -7,20 +7,23 @@
 // 64..127), 64 TMEM columns each.  So every accumulator row is owned by two threads, each holding
 // half of it, and all four softmax warps do useful work on a 64-row tile.
 //
-// Warp roles (448 threads, one CTA per SM):
-//   warps 0-3, 10-13  softmax: two groups of four warps take alternate chunks; inside a group two
-//              threads own half a row (64 scores) each.  Per chunk a thread pulls its scores from tensor memory into registers (which frees the S buffer at once), forms
-//              the row maximum with its partner thread through shared memory, raises the running
-//              maximum lazily (only when a chunk exceeds it by more than 2^8), writes
-//              P = exp2(S*scale - m) in the input dtype into a double-buffered operand tile and
-//              rescales its part of the row of O in the rare chunks where the maximum moved.
-//   warps 4,9  MMA issuers (one thread each): warp 4 issues S_j = Q K_j^T, warp 9 issues O += P_j V_j;
-//              S and P are double buffered, so the tensor pipe works on S_{j+1} and
+// Warp roles (576 threads, one CTA per SM):
+//   warps 0-7  softmax: two groups of four warps (0-3, 4-7) take alternate chunks; inside a group
+//              two threads own half a row (64 scores) each.  Per chunk a thread pulls its scores
+//              from tensor memory into registers (which frees the S buffer at once), forms the row
+//              maximum with its partner thread through shared memory, raises the running maximum
+//              lazily (only when a chunk exceeds it by more than 2^8; the value is shared by both
+//              groups), writes P = exp2(S*scale - m) in the input dtype into a double-buffered
+//              operand tile and rescales its part of the row of O in the rare chunks where the
+//              maximum moved.
+//   warps 8-11  K gather producers, warps 12-15 V gather producers: cp.async 16-byte pieces of the
+//              selected rows into rings of 128-byte-swizzled operand tiles (2 K stages, 3 V
+//              stages); copy completion is reported to the stage's mbarrier asynchronously; index
+//              loads run two chunks ahead and are exchanged inside the warp with shuffles.
+//   warps 16,17  MMA issuers (one thread each): warp 16 issues S_j = Q K_j^T, warp 17 issues
+//              O += P_j V_j; S and P are double buffered, so the tensor pipe works on S_{j+1} and
 //              O += P_{j-1} V_{j-1} while softmax j runs.
-//   warps 5-8  gather producers: cp.async 16-byte pieces of the selected K and V rows into rings of
-//              128-byte-swizzled operand tiles (2 K stages, 3 V stages; K runs a chunk ahead of V);
-//              copy completion is reported to the stage's mbarrier asynchronously, index loads run
-//              further ahead and are exchanged inside the warp with shuffles.
+// The producer warpgroups give registers to the softmax warpgroups (setmaxnreg).
 // Every wait is a bounded mbarrier wait; a timeout sets VA_STATUS_TIMEOUT and unwinds the CTA.
 #include "va_common.cuh"
 #include "va_sm100.cuh"
@@ -45,7 +48,11 @@ constexpr int kKvTile = 128 * 256;  // 128 gathered rows
 constexpr int kQTile = 64 * 256;    // 64 query rows / 64 rows of P
 constexpr int kKStages = 2;  // K tiles are released as soon as S_j has been computed
 constexpr int kVStages = 3;  // V tiles live until O += P_j V_j has completed
-constexpr int kThreads = 448;
+constexpr int kThreads = 576;
+// Registers per thread: the kernel is launched with 96 (the most 18 warps can all have); the two
+// producer warpgroups hand 40 each back and the two softmax warpgroups take them:
+// 256 * 56 + 256 * 136 + 64 * 96 = 576 * 96.
+constexpr int kProducerRegs = 56, kSoftmaxRegs = 136;
 constexpr size_t kSmem = 1024 + (size_t)kQTile * 3 + (size_t)kKvTile * (kKStages + kVStages);  // Q, P x2, K ring, V ring
 constexpr float kRescaleThreshold = 8.0f;                                            // log2 units
 
@@ -53,6 +60,12 @@ struct Barriers {
   uint64_t qfull, kfull[kKStages], kempty[kKStages], vfull[kVStages], vempty[kVStages];
   uint64_t sfull[2], sempty[2], pfull[2], pempty[2], ofull, xch[4], dec[2], fin;
 };
+
+// Register hand-over between warpgroups (four consecutive warps, all of which execute it).
+template <int N>
+__device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // D[tmem] (+)= A[smem] * B[smem], weight-stationary form (M = 64 uses all 128 lanes)
 __device__ __forceinline__ void umma_ws(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -123,7 +136,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     mbar_init(&bars.ofull, 1);
     fence_proxy_async();
   }
-  if (warp == 4) {
+  if (warp == 16) {
     tmem_alloc(&tmem_base_s, 256);
     tmem_relinquish();
   }
@@ -135,29 +148,33 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
 
   bool timed_out = false;
 
-  if (warp >= 5 && warp <= 8) {
-    // ======================= gather producers =======================
-    const int pt = tid - 160;
+  if (warp >= 8 && warp < 16) {
+    // ======================= gather producers (warps 8-11: K and the Q tile, warps 12-15: V) =======================
+    reg_dealloc<kProducerRegs>();
+    const bool is_v = warp >= 12;
+    const int pt = is_v ? tid - 384 : tid - 256;
     const T* qb = static_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
     const T* kb = static_cast<const T*>(p.k) + b * p.k_sb + hkv * p.k_sh;
     const T* vb = static_cast<const T*>(p.v) + b * p.v_sb + hkv * p.v_sh;
     const int32_t* blk = p.blk_idx + trow * p.blk_stride;
     const int32_t* col = p.col_idx + trow * p.col_stride;
+    if (!is_v) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {  // Q tile: rows beyond the sequence are zero
-      const int pce = pt + i * 128, r = pce >> 4, c = pce & 15;
-      const bool ok = row0 + r < p.sq;
-      cp_async16(smem_addr(q_s + tile_off(64, r, c)), qb + (int64_t)(ok ? row0 + r : 0) * p.q_ss + c * 8, ok);
+      for (int i = 0; i < 8; ++i) {  // Q tile: rows beyond the sequence are zero
+        const int pce = pt + i * 128, r = pce >> 4, c = pce & 15;
+        const bool ok = row0 + r < p.sq;
+        cp_async16(smem_addr(q_s + tile_off(64, r, c)), qb + (int64_t)(ok ? row0 + r : 0) * p.q_ss + c * 8, ok);
+      }
+      cp_async_arrive_noinc(&bars.qfull);
+      mbar_arrive(&bars.qfull);
     }
-    cp_async_arrive_noinc(&bars.qfull);
-    mbar_arrive(&bars.qfull);
     // Copy geometry.  A warp covers two key rows per instruction: lanes 0-15 the sixteen 16-byte
     // pieces of row rbase + 8 i, lanes 16-31 those of the next row.  Because the rows of one thread
     // differ by multiples of 8, its swizzled piece position is the same in all of them and the
     // shared-memory destinations are one base address plus i * 1024.
     // Each lane fetches ONE key index per chunk (that of row rbase + 8 * (lane & 15)), one chunk
     // ahead; the sixteen indices a thread needs are then exchanged with warp shuffles.
-    const int pw = warp - 5, hi = lane >> 4, c = lane & 15;
+    const int pw = (pt >> 5), hi = lane >> 4, c = lane & 15;
     const int rbase = 2 * pw + hi;
     const uint32_t dst_off = tile_off(128, rbase, c);
     const int my_slot = rbase + 8 * c;
@@ -187,53 +204,44 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       cp_async_arrive_noinc(full);
       mbar_arrive(full);
     };
-    // K runs one chunk ahead of V: K_{j+1} only needs S_{j-1} to be done, while V_j has to wait for
-    // the PV product three chunks back.  Raw index loads run one more chunk ahead and are only
-    // interpreted an iteration later, so the in-order warp never stalls on them.
-    int kcur[16], knext[16];
-    int raw1 = fetch_raw(0), raw2 = 0;
+    // K and V have producer warps of their own, so neither copy waits behind the other's stage:
+    // a K stage is free as soon as S has been computed from it, a V stage only after the PV
+    // product.  Raw index loads run two chunks ahead and are only interpreted at the top of a
+    // later iteration, so the in-order warp never stalls on them.
     {
-      const int key0 = decode(0, raw1);
-      keys_s[0][my_slot] = key0;
-      spread(key0, kcur);
-      if (nchunks > 1) raw1 = fetch_raw(1);
-      if (nchunks > 2) raw2 = fetch_raw(2);
-      copy_tile(k_s, kb, p.k_ss, kcur, &bars.kfull[0]);  // K_0: the stage is free
-    }
-    for (int j = 0; j < nchunks && !timed_out; ++j) {
-      if (pt == 0) VA_STAMP(0, j);
-      if (j + 1 < nchunks) {
-        const int jn = j + 1, ks = jn % kKStages, ku = jn / kKStages;
-        const int key = decode(jn, raw1);
-        raw1 = raw2;
-        if (j + 3 < nchunks) raw2 = fetch_raw(j + 3);
-        keys_s[jn & 7][my_slot] = key;
-        spread(key, knext);
-        if (!mbar_wait(&bars.kempty[ks], (ku & 1) ^ 1)) { timed_out = true; break; }
-        if (pt == 0) VA_STAMP(1, j);
-        copy_tile(k_s + (size_t)ks * kKvTile, kb, p.k_ss, knext, &bars.kfull[ks]);
-        if (pt == 0) VA_STAMP(2, j);
+      int keys[16];
+      int raw0 = fetch_raw(0), raw1 = nchunks > 1 ? fetch_raw(1) : 0;
+      for (int j = 0; j < nchunks && !timed_out; ++j) {
+        if (pt == 0) VA_STAMP(is_v ? 3 : 0, j);
+        const int key = decode(j, raw0);
+        raw0 = raw1;
+        if (j + 2 < nchunks) raw1 = fetch_raw(j + 2);
+        if (!is_v) keys_s[j & 7][my_slot] = key;
+        spread(key, keys);
+        if (!is_v) {
+          const int ks = j % kKStages, ku = j / kKStages;
+          if (!mbar_wait(&bars.kempty[ks], (ku & 1) ^ 1)) { timed_out = true; break; }
+          if (pt == 0) VA_STAMP(1, j);
+          copy_tile(k_s + (size_t)ks * kKvTile, kb, p.k_ss, keys, &bars.kfull[ks]);
+          if (pt == 0) VA_STAMP(2, j);
+        } else {
+          const int vs = j % kVStages, vu = j / kVStages;
+          if (!mbar_wait(&bars.vempty[vs], (vu & 1) ^ 1)) { timed_out = true; break; }
+          copy_tile(v_s + (size_t)vs * kKvTile, vb, p.v_ss, keys, &bars.vfull[vs]);
+          if (pt == 0) VA_STAMP(4, j);
+        }
       }
-      {
-        const int vs = j % kVStages, vu = j / kVStages;
-        if (!mbar_wait(&bars.vempty[vs], (vu & 1) ^ 1)) { timed_out = true; break; }
-        if (pt == 0) VA_STAMP(3, j);
-        copy_tile(v_s + (size_t)vs * kKvTile, vb, p.v_ss, kcur, &bars.vfull[vs]);
-        if (pt == 0) VA_STAMP(4, j);
-      }
-#pragma unroll
-      for (int i = 0; i < 16; ++i) kcur[i] = knext[i];
     }
     cp_async_commit();
     cp_async_wait<0>();  // nothing of this thread may still be in flight when the CTA retires
-  } else if (warp == 4 || warp == 9) {
+  } else if (warp >= 16) {
     // ======================= MMA issuers =======================
     // Two independent issuing threads, so that neither product waits behind the other's barriers:
     // warp 4 issues S_j = Q K_j^T, warp 9 issues O += P_j V_j.
     if (lane == 0) {
       constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
       bool ok = true;
-      if (warp == 4) {
+      if (warp == 16) {
         constexpr uint32_t idesc_s = umma_idesc(64, 128, in16, 0, 0);
         const uint32_t q_addr = smem_addr(q_s), kr_addr = smem_addr(k_s);
         ok = mbar_wait(&bars.qfull, 0);
@@ -288,7 +296,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     // quarter warp % 4): two threads own half a row each and meet through shared memory.
     // The reference maximum of a row is one value shared by both groups (m_row_s): the decision for
     // chunk g starts from the value left by chunk g - 1, so all P tiles and O stay on one scale.
-    const int grp = warp >= 10 ? 1 : 0;
+    reg_alloc<kSoftmaxRegs>();
+    const int grp = warp >> 2;
     const int qtr = warp & 3;
     const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
     const int tl = qtr * 32 + lane;           // TMEM lane
@@ -437,7 +446,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   if (timed_out && p.status) atomicOr(p.status, VA_STATUS_TIMEOUT);
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, 256);
+  if (warp == 16) tmem_dealloc(tmem, 256);
 }
 
 template <int DT>
