@@ -48,7 +48,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
   __shared__ int keys_s[4][kChunk];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // causal tiles grow with their index: the longest are started first, so the grid's tail is made of short ones
+  const int tile = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int hkv = h / p.rep;
   const int row0 = tile * PQ;
   const int64_t trow = ((int64_t)b * p.heads + h) * p.nq + tile;

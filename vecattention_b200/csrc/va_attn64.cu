@@ -38,9 +38,12 @@ namespace {
 // Build with -DVA_DEBUG_STAMPS to record clock64() time stamps of one CTA's pipeline events.
 #ifdef VA_DEBUG_STAMPS
 __device__ long long g_stamps[32 * 16];
+__device__ long long g_cta_times[4 * 8192];  // per CTA of head 0: SM id, entry, pipeline start, exit (clock64 of that SM)
+#define VA_CTA_TIME(slot) do { if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 8192) { if ((slot) == 0) { unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); g_cta_times[blockIdx.x * 4] = sm; } g_cta_times[blockIdx.x * 4 + 1 + (slot)] = clock64(); } } while (0)
 #define VA_STAMP(ev, j) do { if (blockIdx.x == 7 && blockIdx.y == 0 && (j) < 16) g_stamps[(ev) * 16 + (j)] = clock64(); } while (0)
 #else
 #define VA_STAMP(ev, j) do { } while (0)
+#define VA_CTA_TIME(slot) do { } while (0)
 #endif
 
 constexpr int kChunk = 128;
@@ -90,7 +93,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   __shared__ float fin_s[256];       // [group][TMEM lane]: row sums, added in the epilogue
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  VA_CTA_TIME(0);
+  // causal tiles grow with their index: the longest are started first, so the grid's tail is made of short ones
+  const int tile = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int hkv = h / p.rep;
   const int row0 = tile * PQ;
   const int64_t trow = ((int64_t)b * p.heads + h) * p.nq + tile;
@@ -144,6 +149,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
+  VA_CTA_TIME(1);
   const uint32_t t_s0 = tmem, t_o = tmem + 128;  // S buffers at columns 0 and 64, O at 128 (64 columns each)
 
   bool timed_out = false;
@@ -447,6 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   tc_fence_before();
   __syncthreads();
   if (warp == 16) tmem_dealloc(tmem, 256);
+  VA_CTA_TIME(2);
 }
 
 template <int DT>
@@ -465,6 +472,9 @@ int launch(const AttnParams& p, int batch, cudaStream_t stream) {
 #ifdef VA_DEBUG_STAMPS
 extern "C" int va_debug_read_stamps(long long* host_out) {
   return (int)cudaMemcpyFromSymbol(host_out, g_stamps, sizeof(long long) * 32 * 16);
+}
+extern "C" int va_debug_read_cta_times(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(long long) * 4 * 8192);
 }
 #endif
 

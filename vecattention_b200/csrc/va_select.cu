@@ -8,19 +8,19 @@
 // register, every row's index list comes out ascending and deterministic, and no atomics, no
 // zero-filled buffers and no second pass are needed.
 //
-// Warp roles (448 threads, one CTA per SM):
-//   warps 5-8  producers: cp.async the next K tile (128 contiguous key rows) into a 4-stage ring of
-//              128-byte-swizzled operand tiles; completion is reported to the stage's mbarrier.
-//   warp  4    MMA issuer (one thread): S_t = Q~ K_t^T, 128 x 128 x 128 as eight tcgen05.mma, into
-//              one of two 128-column accumulator buffers in tensor memory.
-//   warps 0-3, 10-13  row walkers: pooled row r = TMEM lane r is owned by two threads, one for
-//              columns 0..63 of the tile (warps 0-3) and one for columns 64..127 (warps 10-13; a warp
-//              reaches the lane quarter warp % 4).  Per tile each pulls its 64 estimates into
-//              registers (freeing the accumulator at once) and forms its key blocks' maxima; the pair
-//              swaps them through shared memory, so both know the running maximum entering every
-//              block; each builds the keep mask fp32(s + gap) >= m of its half, they swap counts, and
-//              each appends its kept keys at its own offset of the row's list.
+// Warp roles (672 threads, one CTA per SM):
+//   warps 0-15  row walkers: pooled row r = TMEM lane r is owned by four threads, one per 32-key
+//              quarter of the tile (warp w walks quarter w / 4 of the rows of lane quarter w % 4,
+//              the only lanes it can reach).  Per tile each pulls its 32 estimates into registers
+//              and forms the maxima of its key blocks; the four swap them through shared memory,
+//              so all know the running maximum entering every block; each builds the keep mask
+//              fp32(s + gap) >= m of its quarter, they swap counts, and each appends its kept keys
+//              at its own offset of the row's list.
 //              (k_local_size 128: one block spans the whole tile; warps 0-3 walk it alone.)
+//   warps 16-19 producers: cp.async the next K tile (128 contiguous key rows) into a 4-stage ring
+//              of 128-byte-swizzled operand tiles; completion is reported to the stage's mbarrier.
+//   warp  20   MMA issuer (one thread): S_t = Q~ K_t^T, 128 x 128 x 128 as eight tcgen05.mma, into
+//              one of two 128-column accumulator buffers in tensor memory.
 // All hand-offs are mbarriers with bounded waits; a timeout sets VA_STATUS_TIMEOUT.
 #include "va_common.cuh"
 #include "va_sm100.cuh"
@@ -59,11 +59,12 @@ constexpr int kRows = 128;   // pooled rows per CTA
 constexpr int kTile = 128;   // keys per tile
 constexpr int kTileBytes = 128 * 256;
 constexpr int kStages = 4;
-constexpr int kThreads = 448;
+constexpr int kThreads = 672;
+constexpr int kWalkerWarps = 16;
 constexpr size_t kSmem = 1024 + (size_t)kTileBytes * (1 + kStages);
 
 struct Barriers {
-  uint64_t kfull[kStages], kempty[kStages], sfull[2], sempty[2], pair[4];
+  uint64_t kfull[kStages], kempty[kStages], sfull[2], sempty[2], quad[4];
 };
 
 // per-row walking state
@@ -96,16 +97,17 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_khi;
-  __shared__ float xmax_s[4 * 2 * 4 * 32];  // [lane quarter][tile half][block][lane]: block maxima swapped by a row's two threads
-  __shared__ int xcnt_s[4 * 2 * 32];         // kept-key counts swapped by a row's two threads
+  __shared__ float xmax_s[4 * 4 * 2 * 32];  // [lane quarter][key quarter][block][lane]: block maxima swapped by a row's four threads
+  __shared__ int xcnt_s[4 * 4 * 32];         // [lane quarter][key quarter][lane]: kept-key counts swapped by a row's four threads
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int hkv = blockIdx.y, b = blockIdx.z;
   const int nrows = p.rep * p.nq;
-  const int row_base = blockIdx.x * kRows;
+  // causal rows walk more keys the later their tile: the longest walks are started first
+  const int row_base = (p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x) * kRows;
 
-  // ---- per-row state: walker threads (warps 0-3 and 10-13) own row (warp % 4) * 32 + lane ----
-  const bool is_walker = warp < 4 || warp >= 10;
+  // ---- per-row state: walker threads (warps 0-15) own row (warp % 4) * 32 + lane ----
+  const bool is_walker = warp < kWalkerWarps;
   const int wrow = (warp & 3) * 32 + lane;
   const int R = row_base + wrow;
   const bool row_ok = is_walker && R < nrows;
@@ -180,12 +182,12 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars.sfull[s], 1);
-      mbar_init(&bars.sempty[s], BK <= 64 ? 256 : 128);
+      mbar_init(&bars.sempty[s], BK <= 64 ? kWalkerWarps * 32 : 128);
     }
-    for (int s = 0; s < 4; ++s) mbar_init(&bars.pair[s], 64);
+    for (int s = 0; s < 4; ++s) mbar_init(&bars.quad[s], 128);
     fence_proxy_async();
   }
-  if (warp == 4) {
+  if (warp == 20) {
     tmem_alloc(&tmem_base_s, 256);
     tmem_relinquish();
   }
@@ -195,16 +197,16 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   const uint32_t tmem = tmem_base_s;
   bool timed_out = false;
 
-  if (warp >= 5 && warp <= 8) {
+  if (warp >= 16 && warp < 20) {
     // ======================= K tile producers =======================
-    const int pw = warp - 5, hh = lane >> 4, c = lane & 15;
+    const int pw = warp - 16, hh = lane >> 4, c = lane & 15;
     const int rbase = 2 * pw + hh;  // this thread copies piece c of rows rbase + 8 i, i = 0..15
     const uint32_t dst_off = tile_off(128, rbase, c);
     const T* kbase = static_cast<const T*>(p.k) + b * p.k_sb + hkv * p.k_sh + c * 8;
     for (int t = t_lo; t < t_hi; ++t) {
       const int n = t - t_lo, s = n % kStages, u = n / kStages;
       if (!mbar_wait(&bars.kempty[s], (u & 1) ^ 1)) { timed_out = true; break; }
-      if (tid == 160) VA_STAMP(0, n);
+      if (tid == 512) VA_STAMP(0, n);
       const uint32_t dst = smem_addr(k_s + (size_t)s * kTileBytes) + dst_off;
       const int key0 = t * kTile + rbase;
       if (t * kTile + kTile <= p.sk) {
@@ -218,13 +220,13 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
       }
       cp_async_arrive_noinc(&bars.kfull[s]);
       mbar_arrive(&bars.kfull[s]);
-      if (tid == 160) VA_STAMP(1, n);
+      if (tid == 512) VA_STAMP(1, n);
     }
     cp_async_commit();
     cp_async_wait<0>();  // nothing of this thread may still be in flight when the CTA retires
-  } else if (warp == 4 || warp == 9) {
-    // ======================= MMA issuer (warp 9 is idle) =======================
-    if (lane == 0 && warp == 4) {
+  } else if (warp == 20) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
       constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
       constexpr uint32_t idesc = umma_idesc(128, 128, in16, 0, 0);
       const uint32_t q_addr = smem_addr(q_s), kr_addr = smem_addr(k_s);
@@ -249,7 +251,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
     }
   } else {
     // ======================= row walkers =======================
-    const int qtr = warp & 3, colh = warp >= 10 ? 1 : 0;
+    const int qtr = warp & 3, cq = warp >> 2;  // TMEM lane quarter, key quarter of the tile
     const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
     Row row;
     row.run_max = -INFINITY;
@@ -267,116 +269,123 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
       return true;
     };
     if constexpr (BK <= 64) {
-      constexpr int NB = 64 / BK;  // key blocks per half tile
+      constexpr int SB = BK < 32 ? BK : 32;  // keys per published maximum
+      constexpr int NP = 32 / SB;            // maxima a thread publishes per tile
+      constexpr int NBT = kTile / BK;        // key blocks per tile
       for (int t = t_lo; t < t_hi; ++t) {
         const int n = t - t_lo, sb = n & 1, ub = n >> 1;
         if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
         tc_fence_after();
         if (tid == 0) VA_STAMP(4, n);
-        const int key_t = t * kTile, key_h = key_t + colh * 64;
-        // ---- my 64 estimates -> registers; the accumulator buffer is free again ----
-        uint32_t v[64];
-        {
-          uint32_t a[32], c[32];
-          const uint32_t t_s = tmem + (uint32_t)sb * 128 + lane_base + colh * 64;
-          tmem_ld32(t_s, a);
-          tmem_ld32(t_s + 32, c);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            v[i] = a[i];
-            v[32 + i] = c[i];
-          }
-        }
+        const int key_t = t * kTile, key_q = key_t + cq * 32;
+        // ---- my 32 estimates -> registers; the accumulator buffer is free again ----
+        uint32_t v[32];
+        tmem_ld32(tmem + (uint32_t)sb * 128 + lane_base + cq * 32, v);
+        tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&bars.sempty[sb]);
         // ---- maxima of my key blocks (keys past the sequence end never count) ----
-        float bm[NB];
-        if (key_h + 64 <= p.sk) {
+        float pm[NP];
+        if (key_q + 32 <= p.sk) {
 #pragma unroll
-          for (int kb = 0; kb < NB; ++kb) {
+          for (int kb = 0; kb < NP; ++kb) {
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < BK; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[kb * BK + j]));
-            bm[kb] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            for (int j = 0; j < SB; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[kb * SB + j]));
+            pm[kb] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
           }
         } else {
 #pragma unroll
-          for (int kb = 0; kb < NB; ++kb) {
-            bm[kb] = -INFINITY;
+          for (int kb = 0; kb < NP; ++kb) {
+            pm[kb] = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < BK; ++j)
-              if (key_h + kb * BK + j < p.sk) bm[kb] = fmaxf(bm[kb], __uint_as_float(v[kb * BK + j]));
+            for (int j = 0; j < SB; ++j)
+              if (key_q + kb * SB + j < p.sk) pm[kb] = fmaxf(pm[kb], __uint_as_float(v[kb * SB + j]));
           }
         }
 #pragma unroll
-        for (int kb = 0; kb < NB; ++kb) xmax_s[((qtr * 2 + colh) * 4 + kb) * 32 + lane] = bm[kb];
-        mbar_arrive(&bars.pair[qtr]);
-        if (!mbar_wait(&bars.pair[qtr], 0)) { timed_out = true; break; }
-        // ---- running maximum entering / after every block of the tile, identical in both threads ----
-        float rm_own[NB];
-        bool on_own[NB];
+        for (int kb = 0; kb < NP; ++kb) xmax_s[((qtr * 4 + cq) * 2 + kb) * 32 + lane] = pm[kb];
+        mbar_arrive(&bars.quad[qtr]);
+        if (!mbar_wait(&bars.quad[qtr], 0)) { timed_out = true; break; }
+        // ---- running maximum entering / after every block of the tile, identical in the four threads ----
+        float rm_own[NP];
+        bool on_own[NP];
 #pragma unroll
-        for (int k = 0; k < 2 * NB; ++k) {
-          const bool mine = (k / NB) == colh;
-          const float m = mine ? bm[k % NB] : xmax_s[((qtr * 2 + (k / NB)) * 4 + (k % NB)) * 32 + lane];
+        for (int k = 0; k < NBT; ++k) {
+          float m;
+          bool mine;
+          if constexpr (BK <= 32) {
+            const int q = k / NP, kb = k % NP;  // the quarter that holds block k and its place there
+            mine = q == cq;
+            m = mine ? pm[kb] : xmax_s[((qtr * 4 + q) * 2 + kb) * 32 + lane];
+          } else {  // a 64-key block spans two quarters
+            mine = k == (cq >> 1);
+            const float m0 = (2 * k == cq) ? pm[0] : xmax_s[((qtr * 4 + 2 * k) * 2) * 32 + lane];
+            const float m1 = (2 * k + 1 == cq) ? pm[0] : xmax_s[((qtr * 4 + 2 * k + 1) * 2) * 32 + lane];
+            m = fmaxf(m0, m1);
+          }
           const bool on = block_begin(key_t + k * BK);
           if (on) row.run_max = fmaxf(row.run_max, m);
           if (mine) {
-            rm_own[k % NB] = row.run_max;
-            on_own[k % NB] = on;
+            rm_own[BK <= 32 ? k % NP : 0] = row.run_max;
+            on_own[BK <= 32 ? k % NP : 0] = on;
           }
         }
-        // ---- keep mask of my 64 keys ----
-        uint32_t mlo[2] = {0u, 0u}, mhi[2] = {0u, 0u};
+        // ---- keep mask of my 32 keys ----
+        uint32_t m2[2] = {0u, 0u};
 #pragma unroll
-        for (int kb = 0; kb < NB; ++kb) {
+        for (int kb = 0; kb < NP; ++kb) {
           if (on_own[kb]) {
 #pragma unroll
-            for (int j = 0; j < BK; ++j) {
-              const int c = kb * BK + j;
-              if (c < 32) keep_bit(mlo[c & 1], __uint_as_float(v[c]), row.gap, rm_own[kb], 1u << c);
-              else keep_bit(mhi[c & 1], __uint_as_float(v[c]), row.gap, rm_own[kb], 1u << (c - 32));
+            for (int j = 0; j < SB; ++j) {
+              const int c = kb * SB + j;
+              keep_bit(m2[c & 1], __uint_as_float(v[c]), row.gap, rm_own[kb], 1u << c);
             }
           }
         }
-        unsigned long long mask = ((unsigned long long)(mhi[0] | mhi[1]) << 32) | (unsigned long long)(mlo[0] | mlo[1]);
-        const int room = row.hi - key_h;  // keys at or past the row's limit are cut off
-        if (room < 64) mask = room <= 0 ? 0ull : (mask & ((1ull << room) - 1ull));
-        const int c_own = __popcll(mask);
-        xcnt_s[(qtr * 2 + colh) * 32 + lane] = c_own;
-        mbar_arrive(&bars.pair[qtr]);
-        if (!mbar_wait(&bars.pair[qtr], 1)) { timed_out = true; break; }
-        const int c_other = xcnt_s[(qtr * 2 + (colh ^ 1)) * 32 + lane];
-        int pos = row.cnt + (colh ? c_other : 0);
-        row.cnt += c_own + c_other;
+        uint32_t mask = m2[0] | m2[1];
+        const int room = row.hi - key_q;  // keys at or past the row's limit are cut off
+        if (room < 32) mask = room <= 0 ? 0u : (mask & ((1u << room) - 1u));
+        const int c_own = __popc(mask);
+        xcnt_s[(qtr * 4 + cq) * 32 + lane] = c_own;
+        mbar_arrive(&bars.quad[qtr]);
+        if (!mbar_wait(&bars.quad[qtr], 1)) { timed_out = true; break; }
+        int before = 0, total = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int cnt_q = q == cq ? c_own : xcnt_s[(qtr * 4 + q) * 32 + lane];
+          if (q < cq) before += cnt_q;
+          total += cnt_q;
+        }
+        int pos = row.cnt + before;
+        row.cnt += total;
         // ---- append my kept keys at my offset of the row's list ----
         if (row.cnt <= p.capacity) {
-          // The first eight kept keys go out as straight-line predicated stores (no divergence: the
+          // The first four kept keys go out as straight-line predicated stores (no divergence: the
           // lanes of a warp keep different numbers of keys), the rare rest in a loop.
           int32_t* wp = row.out + pos;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int j = __ffsll((long long)mask) - 1;
-            st_global_if(wp + e, key_h + j, mask != 0ull);
-            mask &= mask - 1ull;
+          for (int e = 0; e < 4; ++e) {
+            const int j = __ffs((int)mask) - 1;
+            st_global_if(wp + e, key_q + j, mask != 0u);
+            mask &= mask - 1u;
           }
-          wp += 8;
+          wp += 4;
           while (mask) {
-            const int j = __ffsll((long long)mask) - 1;
-            mask &= mask - 1ull;
-            *wp++ = key_h + j;
+            const int j = __ffs((int)mask) - 1;
+            mask &= mask - 1u;
+            *wp++ = key_q + j;
           }
         } else {
           while (mask) {
-            const int j = __ffsll((long long)mask) - 1;
-            mask &= mask - 1ull;
-            if (pos < p.capacity) row.out[pos] = key_h + j;
+            const int j = __ffs((int)mask) - 1;
+            mask &= mask - 1u;
+            if (pos < p.capacity) row.out[pos] = key_q + j;
             ++pos;
           }
         }
       }
-    } else if (colh == 0) {
+    } else if (cq == 0) {
       // k_local_size 128: the block is the whole tile and its maximum is needed before any keep
       // test, so the tile is read twice (maximum pass, then keep pass) by one thread per row
       for (int t = t_lo; t < t_hi; ++t) {
@@ -416,7 +425,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         mbar_arrive(&bars.sempty[sb]);
       }
     }
-    if (row_ok && !timed_out && colh == 0) {  // the row's count is written by the thread of the first half
+    if (row_ok && !timed_out && cq == 0) {  // the row's count is written by the thread of the first quarter
       p.col_count[out_row] = row.cnt;
       if (row.cnt > p.capacity && p.status) atomicOr(p.status, VA_STATUS_OVERFLOW);
     }
@@ -424,7 +433,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   if (timed_out && p.status) atomicOr(p.status, VA_STATUS_TIMEOUT);
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, 256);
+  if (warp == 20) tmem_dealloc(tmem, 256);
 }
 
 template <int DT, int BK>
