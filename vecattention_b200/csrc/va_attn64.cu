@@ -88,6 +88,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int keys_s[8][kChunk];  // ring deep enough that a slot is rewritten long after its last reader
+  __shared__ __align__(16) int mask_s[8][4];  // per chunk and K producer warp: does any of its keys need masking?
   __shared__ float xch_s[2][256];   // [group][phase][TMEM lane]: chunk maxima swapped by a row's two owners
   __shared__ float m_row_s[2][64];   // [chunk parity][row]: the rows' shared reference maxima (exp2 domain)
   __shared__ float fin_s[256];       // [group][TMEM lane]: row sums, added in the epilogue
@@ -222,7 +223,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
         const int key = decode(j, raw0);
         raw0 = raw1;
         if (j + 2 < nchunks) raw1 = fetch_raw(j + 2);
-        if (!is_v) keys_s[j & 7][my_slot] = key;
+        if (!is_v) {
+          keys_s[j & 7][my_slot] = key;
+          // unused slots, and keys that some row of the tile may not see, make the chunk take the masking pass
+          const bool flag = key < 0 || (p.causal && key > p.q_offset + row0);
+          const int any = __any_sync(0xffffffffu, flag);
+          if (lane == 0) mask_s[j & 7][pw] = any;
+        }
         spread(key, keys);
         if (!is_v) {
           const int ks = j % kKStages, ku = j / kKStages;
@@ -316,11 +323,12 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     int xc = 0;
     for (int j = grp; j < nchunks && !timed_out; j += 2) {
       const int sb = grp, ub = j >> 1;
-      const bool masked = p.causal || j == nchunks - 1 || j * kChunk < nblk * 64;
       const int* keys = keys_s[j & 7] + half * 64;
       if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
       tc_fence_after();
       if (tid == 0) VA_STAMP(8, j);
+      const int4 mk = *reinterpret_cast<const int4*>(mask_s[j & 7]);
+      const bool masked = (mk.x | mk.y | mk.z | mk.w) != 0;
       // ---- this thread's 64 scores -> registers; the S buffer is free again right away ----
       uint32_t v[64];
       {
