@@ -284,6 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&bars.sempty[sb]);
+        if (tid == 0) VA_STAMP(5, n);
         // ---- maxima of my key blocks (keys past the sequence end never count) ----
         float pm[NP];
         if (key_q + 32 <= p.sk) {
@@ -306,7 +307,9 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
 #pragma unroll
         for (int kb = 0; kb < NP; ++kb) xmax_s[((qtr * 4 + cq) * 2 + kb) * 32 + lane] = pm[kb];
         mbar_arrive(&bars.quad[qtr]);
+        if (tid == 0) VA_STAMP(6, n);
         if (!mbar_wait(&bars.quad[qtr], 0)) { timed_out = true; break; }
+        if (tid == 0) VA_STAMP(7, n);
         // ---- running maximum entering / after every block of the tile, identical in the four threads ----
         float rm_own[NP];
         bool on_own[NP];
@@ -346,10 +349,12 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         uint32_t mask = m2[0] | m2[1];
         const int room = row.hi - key_q;  // keys at or past the row's limit are cut off
         if (room < 32) mask = room <= 0 ? 0u : (mask & ((1u << room) - 1u));
+        if (tid == 0) VA_STAMP(8, n);
         const int c_own = __popc(mask);
         xcnt_s[(qtr * 4 + cq) * 32 + lane] = c_own;
         mbar_arrive(&bars.quad[qtr]);
         if (!mbar_wait(&bars.quad[qtr], 1)) { timed_out = true; break; }
+        if (tid == 0) VA_STAMP(9, n);
         int before = 0, total = 0;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -384,6 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
             ++pos;
           }
         }
+        if (tid == 0) VA_STAMP(10, n);
       }
     } else if (cq == 0) {
       // k_local_size 128: the block is the whole tile and its maximum is needed before any keep
