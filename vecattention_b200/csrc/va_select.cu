@@ -80,6 +80,26 @@ __device__ __forceinline__ void st_global_if(int32_t* ptr, int value, bool pred)
                : "memory");
 }
 
+// three-input maximum (one instruction)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// maximum of N estimates (N = 16 or 32) as two chains of three-input maxima
+template <int N>
+__device__ __forceinline__ float max_of(const uint32_t* v) {
+  float a = __uint_as_float(v[0]), b = __uint_as_float(v[1]);
+  int i = 2;
+#pragma unroll
+  for (; i + 3 < N; i += 4) {
+    a = fmax3(a, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+    b = fmax3(b, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+  }
+  if (i + 1 < N) a = fmax3(a, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+  return fmaxf(a, b);
+}
+
 // mask |= bit  where  fp32(s + gap) >= run_max   (no branch)
 __device__ __forceinline__ void keep_bit(uint32_t& mask, float s, float gap, float run_max, uint32_t bit) {
   asm("{\n\t.reg .pred p;\n\t.reg .f32 t;\n\t"
@@ -90,6 +110,36 @@ __device__ __forceinline__ void keep_bit(uint32_t& mask, float s, float gap, flo
       : "f"(s), "f"(gap), "f"(run_max), "r"(bit));
 }
 
+// Running maximum for the walker of key quarter CQ on a tile that lies wholly inside the walked key
+// range: only the blocks up to its own last one are visited (the thread of the last quarter ends
+// with the value the next tile starts from and publishes it).  pm = own block maxima, xq = the
+// row's published maxima [quarter][block][lane stride 32], gpos = position of the tile's first
+// block inside its group of G blocks.
+template <int BK, int CQ>
+__device__ __forceinline__ void prefix_interior(const float* pm, const float* xq, float& run_max, int gpos, int G, float* rm_own) {
+  constexpr int NP = BK < 32 ? 32 / BK : 1;
+  constexpr int LAST = BK <= 32 ? (CQ + 1) * NP : CQ / 2 + 1;  // blocks up to and including my last
+#pragma unroll
+  for (int k = 0; k < LAST; ++k) {
+    float m;
+    bool mine;
+    if (BK <= 32) {
+      const int q = k / NP, kb = k % NP;
+      mine = q == CQ;
+      m = mine ? pm[kb] : xq[(q * 2 + kb) * 32];
+    } else {  // a 64-key block spans two quarters
+      mine = k == CQ / 2;
+      const float m0 = (2 * k == CQ) ? pm[0] : xq[(2 * k * 2) * 32];
+      const float m1 = (2 * k + 1 == CQ) ? pm[0] : xq[((2 * k + 1) * 2) * 32];
+      m = fmaxf(m0, m1);
+    }
+    if (gpos == 0) run_max = -INFINITY;  // a new key-block group starts
+    gpos = gpos + 1 == G ? 0 : gpos + 1;
+    run_max = fmaxf(run_max, m);
+    if (mine) rm_own[BK <= 32 ? k % NP : 0] = run_max;
+  }
+}
+
 template <int DT, int BK>
 __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams p) {
   using T = typename Elem<DT>::T;
@@ -98,6 +148,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_khi;
   __shared__ float xmax_s[4 * 4 * 2 * 32];  // [lane quarter][key quarter][block][lane]: block maxima swapped by a row's four threads
+  __shared__ float xrm_s[4 * 32];            // [lane quarter][lane]: running maximum after the tile, from the thread of the last key quarter
   __shared__ int xcnt_s[4 * 4 * 32];         // [lane quarter][key quarter][lane]: kept-key counts swapped by a row's four threads
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -289,12 +340,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         float pm[NP];
         if (key_q + 32 <= p.sk) {
 #pragma unroll
-          for (int kb = 0; kb < NP; ++kb) {
-            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int j = 0; j < SB; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[kb * SB + j]));
-            pm[kb] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-          }
+          for (int kb = 0; kb < NP; ++kb) pm[kb] = max_of<SB>(v + kb * SB);
         } else {
 #pragma unroll
           for (int kb = 0; kb < NP; ++kb) {
@@ -311,42 +357,63 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         if (!mbar_wait(&bars.quad[qtr], 0)) { timed_out = true; break; }
         if (tid == 0) VA_STAMP(7, n);
         // ---- running maximum entering / after every block of the tile, identical in the four threads ----
+        // A tile inside the walked key range (all but the first and last of a CTA) needs no range
+        // tests and lets each thread stop at its own last block.
+        const bool interior = key_t >= lo && key_t + kTile <= k_hi;
         float rm_own[NP];
         bool on_own[NP];
-#pragma unroll
-        for (int k = 0; k < NBT; ++k) {
-          float m;
-          bool mine;
-          if constexpr (BK <= 32) {
-            const int q = k / NP, kb = k % NP;  // the quarter that holds block k and its place there
-            mine = q == cq;
-            m = mine ? pm[kb] : xmax_s[((qtr * 4 + q) * 2 + kb) * 32 + lane];
-          } else {  // a 64-key block spans two quarters
-            mine = k == (cq >> 1);
-            const float m0 = (2 * k == cq) ? pm[0] : xmax_s[((qtr * 4 + 2 * k) * 2) * 32 + lane];
-            const float m1 = (2 * k + 1 == cq) ? pm[0] : xmax_s[((qtr * 4 + 2 * k + 1) * 2) * 32 + lane];
-            m = fmaxf(m0, m1);
+        if (interior) {
+          const float* xq = xmax_s + (qtr * 4 * 2) * 32 + lane;
+          switch (cq) {
+            case 0: prefix_interior<BK, 0>(pm, xq, row.run_max, gpos, G, rm_own); break;
+            case 1: prefix_interior<BK, 1>(pm, xq, row.run_max, gpos, G, rm_own); break;
+            case 2: prefix_interior<BK, 2>(pm, xq, row.run_max, gpos, G, rm_own); break;
+            default: prefix_interior<BK, 3>(pm, xq, row.run_max, gpos, G, rm_own); break;
           }
-          const bool on = block_begin(key_t + k * BK);
-          if (on) row.run_max = fmaxf(row.run_max, m);
-          if (mine) {
-            rm_own[BK <= 32 ? k % NP : 0] = row.run_max;
-            on_own[BK <= 32 ? k % NP : 0] = on;
-          }
-        }
-        // ---- keep mask of my 32 keys ----
-        uint32_t m2[2] = {0u, 0u};
 #pragma unroll
-        for (int kb = 0; kb < NP; ++kb) {
-          if (on_own[kb]) {
+          for (int kb = 0; kb < NP; ++kb) on_own[kb] = true;
+          gpos += NBT;
+          while (gpos >= G) gpos -= G;
+        } else {
 #pragma unroll
-            for (int j = 0; j < SB; ++j) {
-              const int c = kb * SB + j;
-              keep_bit(m2[c & 1], __uint_as_float(v[c]), row.gap, rm_own[kb], 1u << c);
+          for (int k = 0; k < NBT; ++k) {
+            float m;
+            bool mine;
+            if constexpr (BK <= 32) {
+              const int q = k / NP, kb = k % NP;  // the quarter that holds block k and its place there
+              mine = q == cq;
+              m = mine ? pm[kb] : xmax_s[((qtr * 4 + q) * 2 + kb) * 32 + lane];
+            } else {  // a 64-key block spans two quarters
+              mine = k == (cq >> 1);
+              const float m0 = (2 * k == cq) ? pm[0] : xmax_s[((qtr * 4 + 2 * k) * 2) * 32 + lane];
+              const float m1 = (2 * k + 1 == cq) ? pm[0] : xmax_s[((qtr * 4 + 2 * k + 1) * 2) * 32 + lane];
+              m = fmaxf(m0, m1);
+            }
+            const bool on = block_begin(key_t + k * BK);
+            if (on) row.run_max = fmaxf(row.run_max, m);
+            if (mine) {
+              rm_own[BK <= 32 ? k % NP : 0] = row.run_max;
+              on_own[BK <= 32 ? k % NP : 0] = on;
             }
           }
         }
-        uint32_t mask = m2[0] | m2[1];
+        if (cq == 3) xrm_s[qtr * 32 + lane] = row.run_max;  // the value the next tile starts from
+        if (tid == 0) VA_STAMP(11, n);
+        // ---- keep mask of my 32 keys.  fp32(s + gap) >= m  <=>  the difference fp32(s + gap) - m is
+        // not negative (a difference of two floats has the exact sign); its sign bit is shifted
+        // into the mask, last key first, so key c ends up in bit c.  Two additions on the FMA pipe
+        // and one funnel shift per estimate: the integer pipe is the busy one in this kernel. ----
+        uint32_t neg = 0u;
+#pragma unroll
+        for (int c = 31; c >= 0; --c) {
+          const float d = __fsub_rn(__fadd_rn(__uint_as_float(v[c]), row.gap), rm_own[c / SB]);
+          neg = __funnelshift_l(__float_as_uint(d), neg, 1);
+        }
+        if (tid == 0) VA_STAMP(12, n);
+        uint32_t mask = ~neg;
+#pragma unroll
+        for (int kb = 0; kb < NP; ++kb)
+          if (!on_own[kb]) mask &= ~((SB == 32 ? 0xffffffffu : ((1u << SB) - 1u)) << (kb * SB));
         const int room = row.hi - key_q;  // keys at or past the row's limit are cut off
         if (room < 32) mask = room <= 0 ? 0u : (mask & ((1u << room) - 1u));
         if (tid == 0) VA_STAMP(8, n);
@@ -355,6 +422,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         mbar_arrive(&bars.quad[qtr]);
         if (!mbar_wait(&bars.quad[qtr], 1)) { timed_out = true; break; }
         if (tid == 0) VA_STAMP(9, n);
+        row.run_max = xrm_s[qtr * 32 + lane];
         int before = 0, total = 0;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
