@@ -286,3 +286,28 @@ def test_property_linear_in_v(va, big):
     o2 = va.VecAttention_prefill(q, k, v2, 0.6, 64, 16, 8192, False, 4096).float()
     o12 = va.VecAttention_prefill(q, k, (v1.float() + v2.float()).to(v1.dtype), 0.6, 64, 16, 8192, False, 4096).float()
     assert (o12 - (o1 + o2)).abs().max() <= 2 * MAX_ABS
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("pinned", [True, False])
+@pytest.mark.parametrize("slices", [1, 2, 5])
+def test_host_buffer_pipeline_equals_device_call(va, slices, pinned):
+    """VecAttention_prefill_host (host q/k/v, head slices pipelined over three streams) gives the
+    bits of one device call on all heads: GQA, per-head thresholds, causal, two calls in a row
+    sharing the staging buffers."""
+    from vecattention_b200.hostio import VecAttention_prefill_host
+    b, h, hkv, s = 1, 12, 4, 1500
+    staging = {}
+    for seed in (5, 6):
+        q = _rand((b, h, s, 128), seed, torch.bfloat16)
+        k = _rand((b, hkv, s, 128), seed + 10, torch.bfloat16)
+        v = _rand((b, hkv, s, 128), seed + 20, torch.bfloat16)
+        k[:, :, ::23] *= 3.0
+        thr = torch.linspace(0.5, 0.9, h)
+        ref = va.VecAttention_prefill(q.cuda(), k.cuda(), v.cuda(), thr.cuda(), 64, 16, 16, True, 512)
+        hq, hk, hv = (t.pin_memory() if pinned else t for t in (q, k, v))
+        got = VecAttention_prefill_host(hq, hk, hv, thr, 64, 16, 16, True, 512, slices=slices, staging=staging)
+        assert not got.is_cuda and got.shape == q.shape
+        assert torch.equal(got, ref.cpu())
+    with pytest.raises(ValueError):
+        VecAttention_prefill_host(q.cuda(), k, v, 0.5, 64, 16, 16, True, 512)

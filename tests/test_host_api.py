@@ -140,3 +140,25 @@ def test_product_package_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("CPU oracle uses the same association", ""), f
+
+
+def test_host_pipeline_slices_cover_whole_kv_groups(built_library):
+    from vecattention_b200.hostio import head_slices, transfer_bytes
+    for heads, kv, n in [(32, 32, 8), (28, 4, 8), (12, 4, 5), (8, 8, 1), (6, 2, 3)]:
+        parts = head_slices(heads, kv, n)
+        rep = heads // kv
+        assert parts[0][0] == 0 and parts[-1][1] == heads
+        assert all(a1 == b0 for (_, a1), (b0, _) in zip(parts, parts[1:]))
+        assert all((h1 - h0) % rep == 0 and h1 > h0 for h0, h1 in parts)
+        assert len(parts) == min(n, kv)
+    assert transfer_bytes(1, 32, 32, 32768, 32768, 128, 2) == (805306368, 268435456)
+
+
+def test_host_pipeline_fails_loudly_without_a_gpu(built_library):
+    import torch
+    from vecattention_b200.hostio import VecAttention_prefill_host
+    if torch.cuda.is_available():
+        pytest.skip("needs a box without a GPU")
+    q = torch.zeros(1, 2, 64, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        VecAttention_prefill_host(q, q, q, 0.5, 64, 16, 16, False, 64)
