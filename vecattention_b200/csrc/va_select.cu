@@ -100,16 +100,6 @@ __device__ __forceinline__ float max_of(const uint32_t* v) {
   return fmaxf(a, b);
 }
 
-// mask |= bit  where  fp32(s + gap) >= run_max   (no branch)
-__device__ __forceinline__ void keep_bit(uint32_t& mask, float s, float gap, float run_max, uint32_t bit) {
-  asm("{\n\t.reg .pred p;\n\t.reg .f32 t;\n\t"
-      "add.rn.f32 t, %1, %2;\n\t"
-      "setp.ge.f32 p, t, %3;\n\t"
-      "@p or.b32 %0, %0, %4;\n\t}"
-      : "+r"(mask)
-      : "f"(s), "f"(gap), "f"(run_max), "r"(bit));
-}
-
 // Running maximum for the walker of key quarter CQ on a tile that lies wholly inside the walked key
 // range: only the blocks up to its own last one are visited (the thread of the last quarter ends
 // with the value the next tile starts from and publishes it).  pm = own block maxima, xq = the

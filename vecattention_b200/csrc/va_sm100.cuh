@@ -40,6 +40,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // hanging the GPU.
 constexpr int kWaitLimit = 1 << 18;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+#pragma unroll 1  // unrolled, every wait site would carry dozens of copies of the poll
   for (int i = 0; i < kWaitLimit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
