@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       // (in another warp) may not have read it yet.  Both owners write the same value.
       m_row_s[j & 1][row] = m_new;
       mbar_arrive(&bars.dec[grp]);
-      const bool rescale = __any_sync(0xffffffffu, grow && j > 0);  // same rows, hence same verdict, in the partner warp
+      const bool rescale = __any_sync(0xffffffffu, grow && j > 0);  // same rows, hence the same outcome, in the partner warp
       // P buffer free <=> the PV product that read it two chunks ago has completed
       if (!mbar_wait(&bars.pempty[sb], (ub & 1) ^ 1)) { timed_out = true; break; }
       if (rescale) {
