@@ -345,3 +345,25 @@ def vecattention_prefill(q, k, v, threshold=None, q_pooling_size: int = 128,
     if return_selection:
         return out, sel
     return out
+
+
+# --------------------------------------------------------------------------------------
+# The dispatcher's vision-slice composition around the operator
+# --------------------------------------------------------------------------------------
+def vecattention_prefill_vision(q, k, v, threshold, q_pooling_size, k_local_size, group_k_block, chunk_size,
+                                vision_start, vision_end, bsq: int = DEFAULT_BSQ, compat_q1: bool = True):
+    """The ``vecattention`` branch of customize_prefill_attention with vision positions set,
+    spattn/src/models/utils.py:97-128 (causal): full attention on rows [0, vision_start), the
+    operator on [0, vision_end), full attention over all keys on rows [vision_end, S)."""
+    s = q.shape[2]
+    end = s if vision_end is None else vision_end
+    out_va = vecattention_prefill(q[:, :, :end], k[:, :, :end], v[:, :, :end], threshold, q_pooling_size,
+                                  k_local_size, group_k_block, True, chunk_size, bsq=bsq, compat_q1=compat_q1)
+    out_va = out_va.clone()
+    if vision_start is not None:
+        out_va[:, :, :vision_start] = dense_attention(q[:, :, :vision_start], k[:, :, :vision_start],
+                                                      v[:, :, :vision_start], True)
+    if vision_end is not None:
+        after = dense_attention(q[:, :, end:], k, v, True, q_offset=end)
+        return torch.cat([out_va, after.to(out_va.dtype)], dim=2)
+    return out_va

@@ -162,3 +162,17 @@ def test_host_pipeline_fails_loudly_without_a_gpu(built_library):
     q = torch.zeros(1, 2, 64, 128, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
         VecAttention_prefill_host(q, q, q, 0.5, 64, 16, 16, False, 64)
+
+
+def test_dense_block_tables_cover_keys_up_to_the_diagonal(built_library):
+    import torch
+    from vecattention_b200.vision import dense_block_tables
+    for row0, rows in [(0, 64), (37, 100), (1900, 148), (0, 1), (63, 2), (128, 640)]:
+        cnt, start = dense_block_tables(2, 3, row0, rows, "cpu")
+        nq = -(-rows // 64)
+        assert cnt.shape == (2, 3, nq) and start.shape[:3] == (2, 3, nq) and cnt.dtype == torch.int32
+        for t in range(nq):
+            last = min(row0 + 64 * (t + 1), row0 + rows) - 1
+            n = int(cnt[1, 2, t])
+            assert n == last // 64 + 1 and n <= start.shape[3]
+            assert start[1, 2, t, :n].tolist() == [64 * i for i in range(n)]
