@@ -14,8 +14,9 @@
 //              the only lanes it can reach).  Per tile each pulls its 32 estimates into registers
 //              and forms the maxima of its key blocks; the four swap them through shared memory,
 //              so all know the running maximum entering every block; each builds the keep mask
-//              fp32(s + gap) >= m of its quarter, they swap counts, and each appends its kept keys
-//              at its own offset of the row's list.
+//              fp32(s + gap) >= m of its quarter; the counts travel with the next tile's maxima
+//              (one meeting per tile), after which each appends its kept keys at its own offset of
+//              the row's list.
 //              (k_local_size 128: one block spans the whole tile; warps 0-3 walk it alone.)
 //   warps 16-19 producers: cp.async the next K tile (128 contiguous key rows) into a 4-stage ring
 //              of 128-byte-swizzled operand tiles; completion is reported to the stage's mbarrier.
@@ -137,9 +138,10 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_khi;
-  __shared__ float xmax_s[4 * 4 * 2 * 32];  // [lane quarter][key quarter][block][lane]: block maxima swapped by a row's four threads
-  __shared__ float xrm_s[4 * 32];            // [lane quarter][lane]: running maximum after the tile, from the thread of the last key quarter
-  __shared__ int xcnt_s[4 * 4 * 32];         // [lane quarter][key quarter][lane]: kept-key counts swapped by a row's four threads
+  // exchange areas of a row's four threads, double buffered by tile parity (the threads meet once per tile)
+  __shared__ float xmax_s[2][4 * 4 * 2 * 32];  // [parity][lane quarter][key quarter][block][lane]: block maxima
+  __shared__ float xrm_s[2][4 * 32];         // [parity][lane quarter][lane]: running maximum after the tile, from the thread of the last key quarter
+  __shared__ int xcnt_s[2][4 * 4 * 32];      // [parity][lane quarter][key quarter][lane]: kept-key counts
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int hkv = blockIdx.y, b = blockIdx.z;
@@ -313,8 +315,50 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
       constexpr int SB = BK < 32 ? BK : 32;  // keys per published maximum
       constexpr int NP = 32 / SB;            // maxima a thread publishes per tile
       constexpr int NBT = kTile / BK;        // key blocks per tile
+      // The four threads of a row meet once per tile: the meeting that publishes a tile's block
+      // maxima also carries the previous tile's counts (and the running maximum it ended with), so
+      // a tile's kept keys are appended one tile later, after the positions are known.
+      uint32_t prev_mask = 0u;  // keep mask of the previous tile, not yet appended
+      int prev_key = 0, prev_cnt = 0;
+      auto append_prev = [&](int par) {
+        int before = 0, total = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int cnt_q = q == cq ? prev_cnt : xcnt_s[par][(qtr * 4 + q) * 32 + lane];
+          if (q < cq) before += cnt_q;
+          total += cnt_q;
+        }
+        int pos = row.cnt + before;
+        row.cnt += total;
+        uint32_t mask = prev_mask;
+        if (row.cnt <= p.capacity) {
+          // The first four kept keys go out as straight-line predicated stores (no divergence: the
+          // lanes of a warp keep different numbers of keys), the rare rest in a loop.
+          int32_t* wp = row.out + pos;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = __ffs((int)mask) - 1;
+            st_global_if(wp + e, prev_key + j, mask != 0u);
+            mask &= mask - 1u;
+          }
+          wp += 4;
+          while (mask) {
+            const int j = __ffs((int)mask) - 1;
+            mask &= mask - 1u;
+            *wp++ = prev_key + j;
+          }
+        } else {
+          while (mask) {
+            const int j = __ffs((int)mask) - 1;
+            mask &= mask - 1u;
+            if (pos < p.capacity) row.out[pos] = prev_key + j;
+            ++pos;
+          }
+        }
+      };
+      int n_done = 0;
       for (int t = t_lo; t < t_hi; ++t) {
-        const int n = t - t_lo, sb = n & 1, ub = n >> 1;
+        const int n = t - t_lo, sb = n & 1, ub = n >> 1, par = n & 1;
         if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
         tc_fence_after();
         if (tid == 0) VA_STAMP(4, n);
@@ -341,11 +385,16 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
           }
         }
 #pragma unroll
-        for (int kb = 0; kb < NP; ++kb) xmax_s[((qtr * 4 + cq) * 2 + kb) * 32 + lane] = pm[kb];
+        for (int kb = 0; kb < NP; ++kb) xmax_s[par][((qtr * 4 + cq) * 2 + kb) * 32 + lane] = pm[kb];
         mbar_arrive(&bars.quad[qtr]);
         if (tid == 0) VA_STAMP(6, n);
-        if (!mbar_wait(&bars.quad[qtr], 0)) { timed_out = true; break; }
+        if (!mbar_wait(&bars.quad[qtr], par)) { timed_out = true; break; }
         if (tid == 0) VA_STAMP(7, n);
+        if (n > 0) {  // the previous tile: where it ended and where its keys go
+          row.run_max = xrm_s[par ^ 1][qtr * 32 + lane];
+          append_prev(par ^ 1);
+        }
+        if (tid == 0) VA_STAMP(9, n);
         // ---- running maximum entering / after every block of the tile, identical in the four threads ----
         // A tile inside the walked key range (all but the first and last of a CTA) needs no range
         // tests and lets each thread stop at its own last block.
@@ -353,7 +402,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         float rm_own[NP];
         bool on_own[NP];
         if (interior) {
-          const float* xq = xmax_s + (qtr * 4 * 2) * 32 + lane;
+          const float* xq = xmax_s[par] + (qtr * 4 * 2) * 32 + lane;
           switch (cq) {
             case 0: prefix_interior<BK, 0>(pm, xq, row.run_max, gpos, G, rm_own); break;
             case 1: prefix_interior<BK, 1>(pm, xq, row.run_max, gpos, G, rm_own); break;
@@ -372,11 +421,11 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
             if constexpr (BK <= 32) {
               const int q = k / NP, kb = k % NP;  // the quarter that holds block k and its place there
               mine = q == cq;
-              m = mine ? pm[kb] : xmax_s[((qtr * 4 + q) * 2 + kb) * 32 + lane];
+              m = mine ? pm[kb] : xmax_s[par][((qtr * 4 + q) * 2 + kb) * 32 + lane];
             } else {  // a 64-key block spans two quarters
               mine = k == (cq >> 1);
-              const float m0 = (2 * k == cq) ? pm[0] : xmax_s[((qtr * 4 + 2 * k) * 2) * 32 + lane];
-              const float m1 = (2 * k + 1 == cq) ? pm[0] : xmax_s[((qtr * 4 + 2 * k + 1) * 2) * 32 + lane];
+              const float m0 = (2 * k == cq) ? pm[0] : xmax_s[par][((qtr * 4 + 2 * k) * 2) * 32 + lane];
+              const float m1 = (2 * k + 1 == cq) ? pm[0] : xmax_s[par][((qtr * 4 + 2 * k + 1) * 2) * 32 + lane];
               m = fmaxf(m0, m1);
             }
             const bool on = block_begin(key_t + k * BK);
@@ -387,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
             }
           }
         }
-        if (cq == 3) xrm_s[qtr * 32 + lane] = row.run_max;  // the value the next tile starts from
+        if (cq == 3) xrm_s[par][qtr * 32 + lane] = row.run_max;  // the value the next tile starts from
         if (tid == 0) VA_STAMP(11, n);
         // ---- keep mask of my 32 keys.  fp32(s + gap) >= m  <=>  the difference fp32(s + gap) - m is
         // not negative (a difference of two floats has the exact sign); its sign bit is shifted
@@ -407,47 +456,18 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         const int room = row.hi - key_q;  // keys at or past the row's limit are cut off
         if (room < 32) mask = room <= 0 ? 0u : (mask & ((1u << room) - 1u));
         if (tid == 0) VA_STAMP(8, n);
-        const int c_own = __popc(mask);
-        xcnt_s[(qtr * 4 + cq) * 32 + lane] = c_own;
-        mbar_arrive(&bars.quad[qtr]);
-        if (!mbar_wait(&bars.quad[qtr], 1)) { timed_out = true; break; }
-        if (tid == 0) VA_STAMP(9, n);
-        row.run_max = xrm_s[qtr * 32 + lane];
-        int before = 0, total = 0;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int cnt_q = q == cq ? c_own : xcnt_s[(qtr * 4 + q) * 32 + lane];
-          if (q < cq) before += cnt_q;
-          total += cnt_q;
-        }
-        int pos = row.cnt + before;
-        row.cnt += total;
-        // ---- append my kept keys at my offset of the row's list ----
-        if (row.cnt <= p.capacity) {
-          // The first four kept keys go out as straight-line predicated stores (no divergence: the
-          // lanes of a warp keep different numbers of keys), the rare rest in a loop.
-          int32_t* wp = row.out + pos;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = __ffs((int)mask) - 1;
-            st_global_if(wp + e, key_q + j, mask != 0u);
-            mask &= mask - 1u;
-          }
-          wp += 4;
-          while (mask) {
-            const int j = __ffs((int)mask) - 1;
-            mask &= mask - 1u;
-            *wp++ = key_q + j;
-          }
-        } else {
-          while (mask) {
-            const int j = __ffs((int)mask) - 1;
-            mask &= mask - 1u;
-            if (pos < p.capacity) row.out[pos] = key_q + j;
-            ++pos;
-          }
-        }
+        prev_mask = mask;
+        prev_key = key_q;
+        prev_cnt = __popc(mask);
+        xcnt_s[par][(qtr * 4 + cq) * 32 + lane] = prev_cnt;
+        n_done = n + 1;
         if (tid == 0) VA_STAMP(10, n);
+      }
+      // ---- the last tile's keys: one more meeting for its counts ----
+      if (!timed_out && n_done > 0) {
+        mbar_arrive(&bars.quad[qtr]);
+        if (mbar_wait(&bars.quad[qtr], n_done & 1)) append_prev((n_done - 1) & 1);
+        else timed_out = true;
       }
     } else if (cq == 0) {
       // k_local_size 128: the block is the whole tile and its maximum is needed before any keep
