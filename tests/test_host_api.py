@@ -176,3 +176,27 @@ def test_dense_block_tables_cover_keys_up_to_the_diagonal(built_library):
             n = int(cnt[1, 2, t])
             assert n == last // 64 + 1 and n <= start.shape[3]
             assert start[1, 2, t, :n].tolist() == [64 * i for i in range(n)]
+
+
+def test_threshold_files_and_guidance_switch(tmp_path, built_library):
+    import torch
+    from vecattention_b200.thresholds import GuidanceThresholds, load_threshold_matrix, save_threshold_matrix
+    path = str(tmp_path / "thr.json")
+    mat = torch.rand(3, 4)
+    save_threshold_matrix(path, mat, 3, 4)
+    back = load_threshold_matrix(path, 3, 4)
+    assert back.dtype == torch.float32 and back.is_contiguous() and torch.allclose(back, mat)
+    save_threshold_matrix(path, 0.5, 2, 5)
+    assert load_threshold_matrix(path, 2, 5).eq(0.5).all()
+    for layers, heads in [(3, 5), (2, 4)]:  # wrong shape on either axis
+        with pytest.raises(RuntimeError, match="Cannot load threshold file"):
+            load_threshold_matrix(path, layers, heads)
+    with pytest.raises(RuntimeError):
+        load_threshold_matrix(str(tmp_path / "missing.json"), 1, 1)
+    # two passes per diffusion step: positive first, negative on the repeated timestep
+    pos, neg = torch.full((2, 4), 0.9), torch.full((2, 4), 0.6)
+    g = GuidanceThresholds(pos, neg)
+    picks = [g.select(t) is pos for t in (999.0, 999.0, 950.0, 950.0, 900.0)]
+    assert picks == [True, False, True, False, True] and g.step == 3
+    assert g.for_layer(1).shape == (4,) and g.for_layer(1).eq(0.9).all()
+    assert GuidanceThresholds(0.7, guidance=False).select(1.0) == 0.7
