@@ -111,6 +111,8 @@ int va_select(const va_select_args* args, va_stream_t stream);
  *   blk_count  (B,H,nq) int32, blk_idx (B,H,nq,blk_stride) int32 (may be NULL when no blocks)
  *   col_count  (B,H,nq) int32, col_idx (B,H,nq,col_stride) int32
  *   softmax_scale 0 selects 1/sqrt(D).  A tile with no key at all writes zeros.
+ *   lse        optional (B,H,Sq) float32 contiguous: natural-log sum of exp(score * scale) over the
+ *              row's visible keys (the reference API's return_softmax_lse); -inf for a row without keys.
  *   Indices must satisfy 0 <= idx < Sk. */
 typedef struct {
   int32_t dtype, batch, heads, kv_heads, sq, sk, head_dim, pq;
@@ -125,6 +127,7 @@ typedef struct {
   int64_t col_stride;
   float softmax_scale;
   int32_t* status; /* optional device word receiving VA_STATUS_* bits */
+  float* lse;      /* optional, see above */
 } va_attn_args;
 int va_sparse_attn(const va_attn_args* args, va_stream_t stream);
 

@@ -367,3 +367,53 @@ def vecattention_prefill_vision(q, k, v, threshold, q_pooling_size, k_local_size
         after = dense_attention(q[:, :, end:], k, v, True, q_offset=end)
         return torch.cat([out_va, after.to(out_va.dtype)], dim=2)
     return out_va
+
+
+# --------------------------------------------------------------------------------------
+# The threshold tuner's inner loop
+# --------------------------------------------------------------------------------------
+def seg_pr_per_head(q, k, block_size_q, block_size_k=16, group_size_k=16, threshold=None,
+                    chunk_size=8 * 1024, causal=False, bsq: int = DEFAULT_BSQ, round_probs: bool = False):
+    """Recall and sparsity of the selection per head, spattn/threshold/model_tuner.py:118-226:
+    dense softmax over all (visible) keys, masked with the selection (64-key blocks of the block
+    tables in full width, selected columns), summed per row; sparsity = mean over rows of
+    1 - |mask row| / visible keys.  ``round_probs`` rounds each probability to the input dtype
+    before the sum, as the reference does."""
+    b_, h_, s, d = q.shape
+    sk = k.shape[2]
+    rep = h_ // k.shape[1]
+    if isinstance(threshold, torch.Tensor):
+        gap = -torch.log(threshold.float())
+    else:
+        gap = -math.log(threshold)
+    pq = block_size_q
+    blk_count, blk_idx = block_tables(b_, h_, s, pq, causal)
+    recalls = torch.zeros(b_, h_, s, dtype=torch.float64)
+    sparsity = torch.zeros(h_, dtype=torch.float64)
+    kk = k.double().repeat_interleave(rep, dim=1)
+    for i in range(0, s, chunk_size):
+        qc = q[:, :, i:i + chunk_size]
+        n = qc.shape[2]
+        cc, ci = select_columns(pool_q(qc, pq), k, i // pq, gap, causal, pq, block_size_k, wo_initial=causal,
+                                group_k_block=group_size_k, bsq=bsq)
+        scores = (qc.double() @ kk.transpose(-1, -2)) / math.sqrt(d)
+        rows = i + torch.arange(n)
+        see = torch.ones(n, sk, dtype=torch.bool)
+        if causal:
+            see = torch.arange(sk).view(1, -1) <= rows.view(-1, 1)
+            scores = scores.masked_fill(~see, float("-inf"))
+        probs = torch.softmax(scores, dim=-1)
+        if round_probs:
+            probs = probs.to(q.dtype).double()
+        for bb in range(b_):
+            for hh in range(h_):
+                mask = torch.zeros(n, sk, dtype=torch.bool)
+                for t in range(math.ceil(n / pq)):
+                    g = i // pq + t
+                    r0, r1 = t * pq, min((t + 1) * pq, n)
+                    for o in blk_idx[bb, hh, g, : int(blk_count[bb, hh, g])].tolist():
+                        mask[r0:r1, o:min(o + 64, sk)] = True
+                    mask[r0:r1, ci[bb, hh, t, : int(cc[bb, hh, t])].long()] = True
+                recalls[bb, hh, i:i + n] = (probs[bb, hh] * mask).sum(-1)
+                sparsity[hh] += (1.0 - (mask.sum(-1).double() / see.sum(-1).double())).mean() * n
+    return recalls.sum(dim=(0, 2)) / (b_ * s), sparsity / b_ / s

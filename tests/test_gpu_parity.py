@@ -331,3 +331,38 @@ def test_vision_slice_composition_matches_oracle(va, vs, ve):
     assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS, (err.max().item(), err.mean().item())
     with pytest.raises(ValueError):
         va.VecAttention_prefill_vision(q.cuda(), k.cuda(), v.cuda(), 0.7, 64, 16, 16, False, 1024, vision_start_position=3)
+
+
+# ---------------------------------------------------------------------------------------------
+def test_softmax_lse_output(va):
+    """return_softmax_lse of the sparse attention entry point: log-sum-exp of the scaled scores over
+    the keys each row visits; with every key listed it equals the dense value."""
+    b, h, hkv, s = 1, 4, 2, 700
+    q = _rand((b, s, h, 128), 41, torch.bfloat16).cuda()
+    k = _rand((b, s, hkv, 128), 42, torch.bfloat16).cuda()
+    v = _rand((b, s, hkv, 128), 43, torch.bfloat16).cuda()
+    for pq in (64, 128):
+        nq = math.ceil(s / pq)
+        cnt = torch.full((b, h, nq), s, dtype=torch.int32, device="cuda")
+        idx = torch.arange(s, dtype=torch.int32, device="cuda").expand(b, h, nq, s).contiguous()
+        out, lse = va.sparse_attn_func(q, k, v, pq, None, None, cnt, idx, return_softmax_lse=True, causal=False)
+        kk = k.float().repeat_interleave(h // hkv, dim=2)
+        ref = torch.logsumexp(torch.einsum("bqhd,bkhd->bhqk", q.float(), kk) / math.sqrt(128), dim=-1)
+        assert lse.shape == (b, h, s) and lse.dtype == torch.float32
+        assert (lse - ref).abs().max() <= 2e-3, (pq, (lse - ref).abs().max().item())
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_selection_recall_and_sparsity_match_the_tuner_rule(va, causal):
+    from vecattention_b200.recall import selection_recall_sparsity
+    b, h, hkv, s = 1, 4, 4, 1100
+    q = _rand((b, h, s, 128), 61, torch.bfloat16)
+    k = _rand((b, hkv, s, 128), 62, torch.bfloat16)
+    k[:, :, ::17] *= 3.0
+    thr = torch.tensor([0.3, 0.5, 0.7, 0.9])
+    ref_recall, ref_sparsity = O.seg_pr_per_head(q, k, 64, 16, 16, thr, 512, causal)
+    recall, sparsity = selection_recall_sparsity(q.cuda(), k.cuda(), 64, 16, 16, thr.cuda(), 512, causal)
+    assert recall.shape == (h,) and sparsity.shape == (h,)
+    assert (recall.cpu().double() - ref_recall).abs().max() <= 2e-3, (recall, ref_recall)
+    assert (sparsity.cpu().double() - ref_sparsity).abs().max() <= 1e-3, (sparsity, ref_sparsity)
+    assert (recall.cpu()[1:] <= recall.cpu()[:-1] + 1e-3).all()  # a higher threshold keeps less mass

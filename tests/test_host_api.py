@@ -36,7 +36,7 @@ def test_struct_layout_matches_header(lib):
     assert C.sizeof(lib.Tensor4) == 32
     assert C.sizeof(lib.PoolArgs) == 24 + 32 + 8
     assert C.sizeof(lib.SelectArgs) == 56 + 8 + 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8
-    assert C.sizeof(lib.AttnArgs) == 40 + 4 * 32 + 8 * 6 + 8 + 8
+    assert C.sizeof(lib.AttnArgs) == 40 + 4 * 32 + 8 * 6 + 8 + 8 + 8
     assert C.sizeof(lib.PrefillArgs) == 56 + 4 * 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8
 
 

@@ -148,18 +148,19 @@ def sparse_attn_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_poolin
                      softmax_scale: Optional[float] = None) -> torch.Tensor:
     """Vector-sparse attention in the reference's calling convention: ``q`` (B,Sq,H,D), ``k``/``v``
     (B,Sk,Hkv,D), tables per (B,H,ceil(Sq/q_pooling_size)); returns (B,Sq,H,D).  With ``causal``
-    the queries are the last ``Sq`` positions of the ``Sk`` keys."""
-    if return_softmax_lse:
-        raise NotImplementedError("return_softmax_lse is not used on the VecAttention path")
+    the queries are the last ``Sq`` positions of the ``Sk`` keys.  ``return_softmax_lse`` adds the
+    (B,H,Sq) float32 log-sum-exp of the scaled scores over each row's keys."""
+    lse = (torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
+           if return_softmax_lse else None)
     out = _sparse_attn_bhsd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), q_pooling_size,
                             block_count, block_offset, column_count, column_index, causal,
                             q_offset=(k.shape[1] - q.shape[1]) if causal else 0, softmax_scale=softmax_scale,
-                            out_layout="bshd")
-    return out
+                            out_layout="bshd", lse=lse)
+    return (out, lse) if return_softmax_lse else out
 
 
 def _sparse_attn_bhsd(q, k, v, pq, block_count, block_offset, column_count, column_index, causal,
-                      q_offset=0, softmax_scale=None, out=None, out_layout="bhsd", status=None):
+                      q_offset=0, softmax_scale=None, out=None, out_layout="bhsd", status=None, lse=None):
     dev = _require_cuda(q, k, v, column_count, column_index)
     b, h, sq, d = q.shape
     hkv, sk = k.shape[1], k.shape[2]
@@ -189,7 +190,10 @@ def _sparse_attn_bhsd(q, k, v, pq, block_count, block_offset, column_count, colu
                       _t4(q), _t4(k), _t4(v), _t4(out), bc, bo, bs,
                       column_count.data_ptr(), column_index.data_ptr(), col_stride,
                       float(softmax_scale) if softmax_scale else 0.0,
-                      status.data_ptr() if status is not None else None)
+                      status.data_ptr() if status is not None else None,
+                      lse.data_ptr() if lse is not None else None)
+    if lse is not None and (lse.dtype != torch.float32 or not lse.is_contiguous() or tuple(lse.shape) != (b, h, sq)):
+        raise VecAttentionArgumentError("lse must be a contiguous float32 tensor shaped (B, H, Sq)")
     with torch.cuda.device(dev):
         _check(L.lib().va_sparse_attn(C.byref(args), _stream()))
     return out.transpose(1, 2) if out_layout == "bshd" else out

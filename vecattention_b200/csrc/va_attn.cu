@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
       const int r = i >> 4, c = i & 15;
       if (row0 + r < p.sq) *reinterpret_cast<uint4*>(ob + (int64_t)(row0 + r) * p.o_ss + c * 8) = make_uint4(0, 0, 0, 0);
     }
+    if (p.lse && tid < PQ && row0 + tid < p.sq) p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + tid] = -INFINITY;
     return;
   }
 
@@ -315,6 +316,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) sparse_attn_kernel(const Attn
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const bool row_ok = row < PQ && row0 + row < p.sq;
+      if (p.lse && row_ok)  // m_used is in the exp2 domain
+        p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + row] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
       T* orow = ob + (int64_t)(row0 + (row_ok ? row : 0)) * p.o_ss;
 #pragma unroll 1
       for (int qd = 0; qd < 4; ++qd) {
@@ -365,6 +368,7 @@ int sparse_attn(const va_attn_args& a, cudaStream_t stream) {
   p.blk_idx = a.blk_idx; p.blk_stride = a.blk_stride;
   p.col_count = a.col_count; p.col_idx = a.col_idx; p.col_stride = a.col_stride;
   p.status = a.status;
+  p.lse = a.lse;
   p.heads = a.heads; p.rep = a.heads / a.kv_heads; p.sq = a.sq; p.sk = a.sk;
   p.nq = (a.sq + a.pq - 1) / a.pq;
   p.causal = a.causal; p.q_offset = a.q_offset;

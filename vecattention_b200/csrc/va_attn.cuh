@@ -18,6 +18,7 @@ struct AttnParams {
   const int32_t* col_idx;
   int64_t col_stride;
   int32_t* status;
+  float* lse;  // optional (B,H,sq): natural-log sum of exp over the row's keys
   int heads, rep, sq, sk, nq;
   int causal, q_offset;
   float scale_log2;  // softmax_scale * log2(e)

@@ -111,6 +111,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       const int r = i >> 4, c = i & 15;
       if (row0 + r < p.sq) *reinterpret_cast<uint4*>(ob + (int64_t)(row0 + r) * p.o_ss + c * 8) = make_uint4(0, 0, 0, 0);
     }
+    if (p.lse && tid < PQ && row0 + tid < p.sq) p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + tid] = -INFINITY;
     return;
   }
 
@@ -436,6 +437,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
         l = (fin_s[tl] + fin_s[tl ^ 64]) + (fin_s[128 + tl] + fin_s[128 + (tl ^ 64)]);
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const bool row_ok = row0 + row < p.sq;
+        if (p.lse && row_ok && grp == 0 && half == 0)  // one of the row's four owners; m is in the exp2 domain
+          p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + row] = l > 0.f ? (m_fin + log2f(l)) * 0.6931471805599453f : -INFINITY;
         // the two groups split the 64 columns of a lane: group 0 writes the lower 32, group 1 the upper
         T* orow = ob + (int64_t)(row0 + (row_ok ? row : 0)) * p.o_ss + half * 64 + grp * 32;
         uint32_t o[32];
