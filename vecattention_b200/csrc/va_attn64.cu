@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   } else if (warp >= 16) {
     // ======================= MMA issuers =======================
     // Two independent issuing threads, so that neither product waits behind the other's barriers:
-    // warp 4 issues S_j = Q K_j^T, warp 9 issues O += P_j V_j.
+    // warp 16 issues S_j = Q K_j^T, warp 17 issues O += P_j V_j.
     if (lane == 0) {
       constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
       bool ok = true;
@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   } else {
     // ======================= softmax / correction / epilogue =======================
     // Two groups of four warps work on alternate chunks (group 0 = warps 0-3 the even ones, group 1
-    // = warps 10-13 the odd ones), so the latencies of one chunk's softmax (tensor-memory load,
+    // = warps 4-7 the odd ones), so the latencies of one chunk's softmax (tensor-memory load,
     // maximum exchange, exponentials, shared-memory stores) overlap the other's.  Inside a group,
     // accumulator row r lives in TMEM lanes r and 64 + r (64 columns each; a warp reaches the lane
     // quarter warp % 4): two threads own half a row each and meet through shared memory.
