@@ -23,9 +23,8 @@ import json
 import math
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
+import threading
 import time
 
 import torch
@@ -55,54 +54,60 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of one GPU, read through NVML every few milliseconds by a
+    background thread while the warm-up and the timed region run (reading only; nothing is set)."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.path = index, None, None
+    def __init__(self, index: int, period_s: float = 0.003):
+        self.index, self.period = index, period_s
+        self.samples, self.bits, self.max_mhz = [], 0, None
+        self.thread, self.stop, self.nvml, self.handle = None, threading.Event(), None, None
 
     def __enter__(self):
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200", "-f", self.path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            try:  # the CUDA device's own identity, so that CUDA_VISIBLE_DEVICES renumbering cannot mislead
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:  # noqa: BLE001
+                vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+                ids = [v for v in vis.split(",") if v.strip().isdigit()]
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(int(ids[self.index]) if self.index < len(ids) else self.index)
+            self.nvml = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001 - no NVML: the summary says so
+            self.nvml = None
         return self
 
-    def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
+    def _run(self):
+        n = self.nvml
+        reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop.is_set():
             try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+                self.samples.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+                self.bits |= int(reasons(self.handle))
+            except Exception:  # noqa: BLE001
+                pass
+            self.stop.wait(self.period)
+
+    def __exit__(self, *exc):
+        self.stop.set()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        try:
-            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
-            os.unlink(self.path)
-        except (OSError, TypeError):
-            return out
-        sm, reasons = [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in rows:
-            try:
-                sm.append(float(r[0]))
-                out["sm_max_mhz"] = float(r[1])
-            except (ValueError, IndexError):
-                continue
-            for n, val in zip(names, r[2:6]):
-                if val.strip().lower() == "active":
-                    reasons.add(n)
-        if sm:
-            out["sm_mhz"] = statistics.median(sm)
-            out["samples"] = len(sm)
-        out["reasons"] = sorted(reasons)
+        out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": []}
+        if self.samples:
+            out["sm_mhz"] = statistics.median(self.samples)
+            out["sm_min_mhz"] = min(self.samples)
+            out["samples"] = len(self.samples)
+        out["reasons"] = sorted(name for bit, name in self.REASONS.items() if self.bits & bit)
+        if self.nvml is None:
+            out["note"] = "NVML not available"
         return out
 
 
@@ -274,7 +279,6 @@ def graft_arm(args):
 
     # ---- timed region: exactly K steps, device time, max over ranks ----
     with ClockSampler(local_rank) as clk:
-        time.sleep(0.3)  # let the sampler come up; it then covers warm-up and the timed region
         for _ in range(args.warmup):
             step()
         barrier()
