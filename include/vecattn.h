@@ -99,6 +99,10 @@ typedef struct {
                           compat_bsq rule restarts at every chunk boundary; 0: avg_q is one chunk */
 } va_select_args;
 int va_select(const va_select_args* args, va_stream_t stream);
+/* Scratch va_select needs besides its outputs: none (bytes = 0).  Present so that a binding written
+ * against a workspace-query convention has something to call; the reference's wrapper allocates a
+ * zero-filled index buffer and a padded K copy per call (vecattention_kernels.py:104-136). */
+int va_select_workspace_bytes(const va_select_args* args, size_t* bytes);
 
 /* ---- vector-sparse flash attention --------------------------------------------------------------
  * Replaces vllm_flash_attn.sparse_attn_func(q, k, v, q_pooling_size, block_count, block_offset,
@@ -130,6 +134,9 @@ typedef struct {
   float* lse;      /* optional, see above */
 } va_attn_args;
 int va_sparse_attn(const va_attn_args* args, va_stream_t stream);
+/* Scratch va_sparse_attn needs besides its outputs: none (bytes = 0); the reference call site makes
+ * three transposed copies of q, k and v first (spattn/src/VecAttention.py:110-113). */
+int va_sparse_attn_workspace_bytes(const va_attn_args* args, size_t* bytes);
 
 /* ---- dense 64-key block tables -----------------------------------------------------------------
  * Replaces the table construction in VecAttention_prefill, spattn/src/VecAttention.py:62-92:

@@ -200,3 +200,12 @@ def test_threshold_files_and_guidance_switch(tmp_path, built_library):
     assert picks == [True, False, True, False, True] and g.step == 3
     assert g.for_layer(1).shape == (4,) and g.for_layer(1).eq(0.9).all()
     assert GuidanceThresholds(0.7, guidance=False).select(1.0) == 0.7
+
+
+def test_stage_workspace_queries_report_no_scratch(lib):
+    import ctypes as C
+    n = C.c_size_t(123)
+    assert lib.lib().va_select_workspace_bytes(C.byref(lib.SelectArgs()), C.byref(n)) == 0 and n.value == 0
+    n = C.c_size_t(123)
+    assert lib.lib().va_sparse_attn_workspace_bytes(C.byref(lib.AttnArgs()), C.byref(n)) == 0 and n.value == 0
+    assert lib.lib().va_select_workspace_bytes(None, C.byref(n)) == -1

@@ -15,8 +15,9 @@ VA_STATUS_OVERFLOW = 1
 VA_STATUS_TIMEOUT = 2
 
 # every symbol include/vecattn.h declares
-EXPORTS = ("va_pool_q", "va_select", "va_sparse_attn", "va_block_tables", "va_prefill_workspace_bytes",
-           "va_prefill", "va_prefill_static", "va_status_string", "va_version")
+EXPORTS = ("va_pool_q", "va_select", "va_select_workspace_bytes", "va_sparse_attn", "va_sparse_attn_workspace_bytes",
+           "va_block_tables", "va_prefill_workspace_bytes", "va_prefill", "va_prefill_static", "va_status_string",
+           "va_version")
 VA_STATIC_SCRATCH_BYTES = 32 << 20
 
 
@@ -80,6 +81,8 @@ def lib() -> C.CDLL:
     handle.va_pool_q.argtypes = [C.POINTER(PoolArgs), C.c_void_p]
     handle.va_select.argtypes = [C.POINTER(SelectArgs), C.c_void_p]
     handle.va_sparse_attn.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+    handle.va_select_workspace_bytes.argtypes = [C.POINTER(SelectArgs), C.POINTER(C.c_size_t)]
+    handle.va_sparse_attn_workspace_bytes.argtypes = [C.POINTER(AttnArgs), C.POINTER(C.c_size_t)]
     handle.va_block_tables.argtypes = [C.c_int32] * 5 + [C.c_void_p, C.c_void_p, C.c_void_p]
     handle.va_prefill_workspace_bytes.argtypes = [C.POINTER(PrefillArgs), C.POINTER(C.c_size_t)]
     handle.va_prefill.argtypes = [C.POINTER(PrefillArgs), C.c_void_p]

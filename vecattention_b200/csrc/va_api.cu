@@ -125,6 +125,18 @@ int va_select(const va_select_args* a, va_stream_t stream) {
   return select(*a, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int va_select_workspace_bytes(const va_select_args* a, size_t* bytes) {
+  if (!a || !bytes) return VA_ERR_NULL;
+  *bytes = 0;  // the kernel keeps its state in registers, shared and tensor memory
+  return VA_OK;
+}
+
+int va_sparse_attn_workspace_bytes(const va_attn_args* a, size_t* bytes) {
+  if (!a || !bytes) return VA_ERR_NULL;
+  *bytes = 0;
+  return VA_OK;
+}
+
 int va_sparse_attn(const va_attn_args* a, va_stream_t stream) {
   if (!a || !a->col_count || !a->col_idx) return VA_ERR_NULL;
   if (a->blk_count && !a->blk_idx) return VA_ERR_NULL;
