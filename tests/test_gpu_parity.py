@@ -100,6 +100,9 @@ def test_select_parity_golden_inputs(va, name):
     dict(h=2, hkv=1, sq=512, sk=1536, pq=128, bk=32, g=3, causal=False, toff=0, th=0.55),
     dict(h=1, hkv=1, sq=384, sk=2048, pq=64, bk=64, g=2, causal=False, toff=0, th=0.5),
     dict(h=1, hkv=1, sq=256, sk=2048, pq=128, bk=128, g=1, causal=False, toff=0, th=0.5),
+    dict(h=2, hkv=2, sq=1536, sk=1536, pq=128, bk=128, g=1, causal=True, toff=0, th=0.5),   # the reference's default sizes
+    dict(h=2, hkv=1, sq=1100, sk=1100, pq=128, bk=128, g=3, causal=True, toff=0, th=0.6),   # ragged, groups of 3 blocks
+    dict(h=2, hkv=2, sq=1280, sk=1280, pq=128, bk=64, g=2, causal=True, toff=0, th=0.5),
     dict(h=2, hkv=2, sq=512, sk=2048, pq=64, bk=16, g=16, causal=True, toff=24, th=0.4),    # a later chunk
     dict(h=6, hkv=2, sq=4480, sk=4480, pq=64, bk=16, g=16, causal=True, toff=0, th=0.7),     # rows span CTAs/heads
 ])
@@ -193,6 +196,7 @@ PREFILL_CASES = [
     dict(b=1, h=2, hkv=2, s=1200, pq=64, bk=16, g=16, causal=True, chunk=512, th=0.5),
     dict(b=2, h=4, hkv=2, s=1008, pq=128, bk=32, g=4, causal=True, chunk=16384, th=0.6),
     dict(b=1, h=3, hkv=3, s=640, pq=64, bk=16, g=2, causal=False, chunk=256, th=(0.3, 0.5, 0.7)),
+    dict(b=1, h=2, hkv=2, s=1500, pq=128, bk=128, g=1, causal=True, chunk=16384, th=0.5),  # the reference's defaults
 ]
 
 

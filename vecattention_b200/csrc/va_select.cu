@@ -17,7 +17,8 @@
 //              fp32(s + gap) >= m of its quarter; the counts travel with the next tile's maxima
 //              (one meeting per tile), after which each appends its kept keys at its own offset of
 //              the row's list.
-//              (k_local_size 128: one block spans the whole tile; warps 0-3 walk it alone.)
+//              (Blocks of 64 or 128 keys span two or four quarters: their maximum is formed from the
+//              quarters' published maxima.)
 //   warps 16-19 producers: cp.async the next K tile (128 contiguous key rows) into a 4-stage ring
 //              of 128-byte-swizzled operand tiles; completion is reported to the stage's mbarrier.
 //   warp  20   MMA issuer (one thread): S_t = Q~ K_t^T, 128 x 128 x 128 as eight tcgen05.mma, into
@@ -109,7 +110,8 @@ __device__ __forceinline__ float max_of(const uint32_t* v) {
 template <int BK, int CQ>
 __device__ __forceinline__ void prefix_interior(const float* pm, const float* xq, float& run_max, int gpos, int G, float* rm_own) {
   constexpr int NP = BK < 32 ? 32 / BK : 1;
-  constexpr int LAST = BK <= 32 ? (CQ + 1) * NP : CQ / 2 + 1;  // blocks up to and including my last
+  constexpr int QPB = BK <= 32 ? 1 : BK / 32;                   // key quarters per block (blocks of 64 or 128 keys span several)
+  constexpr int LAST = BK <= 32 ? (CQ + 1) * NP : CQ / QPB + 1;  // blocks up to and including my last
 #pragma unroll
   for (int k = 0; k < LAST; ++k) {
     float m;
@@ -118,11 +120,14 @@ __device__ __forceinline__ void prefix_interior(const float* pm, const float* xq
       const int q = k / NP, kb = k % NP;
       mine = q == CQ;
       m = mine ? pm[kb] : xq[(q * 2 + kb) * 32];
-    } else {  // a 64-key block spans two quarters
-      mine = k == CQ / 2;
-      const float m0 = (2 * k == CQ) ? pm[0] : xq[(2 * k * 2) * 32];
-      const float m1 = (2 * k + 1 == CQ) ? pm[0] : xq[((2 * k + 1) * 2) * 32];
-      m = fmaxf(m0, m1);
+    } else {  // the block spans QPB quarters
+      mine = k == CQ / QPB;
+      m = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < QPB; ++i) {
+        const int q = k * QPB + i;
+        m = fmaxf(m, q == CQ ? pm[0] : xq[(q * 2) * 32]);
+      }
     }
     if (gpos == 0) run_max = -INFINITY;  // a new key-block group starts
     gpos = gpos + 1 == G ? 0 : gpos + 1;
@@ -225,7 +230,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars.sfull[s], 1);
-      mbar_init(&bars.sempty[s], BK <= 64 ? kWalkerWarps * 32 : 128);
+      mbar_init(&bars.sempty[s], kWalkerWarps * 32);
     }
     for (int s = 0; s < 4; ++s) mbar_init(&bars.quad[s], 128);
     fence_proxy_async();
@@ -311,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
       gpos = gpos + 1 == G ? 0 : gpos + 1;
       return true;
     };
-    if constexpr (BK <= 64) {
+    {
       constexpr int SB = BK < 32 ? BK : 32;  // keys per published maximum
       constexpr int NP = 32 / SB;            // maxima a thread publishes per tile
       constexpr int NBT = kTile / BK;        // key blocks per tile
@@ -422,11 +427,15 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
               const int q = k / NP, kb = k % NP;  // the quarter that holds block k and its place there
               mine = q == cq;
               m = mine ? pm[kb] : xmax_s[par][((qtr * 4 + q) * 2 + kb) * 32 + lane];
-            } else {  // a 64-key block spans two quarters
-              mine = k == (cq >> 1);
-              const float m0 = (2 * k == cq) ? pm[0] : xmax_s[par][((qtr * 4 + 2 * k) * 2) * 32 + lane];
-              const float m1 = (2 * k + 1 == cq) ? pm[0] : xmax_s[par][((qtr * 4 + 2 * k + 1) * 2) * 32 + lane];
-              m = fmaxf(m0, m1);
+            } else {  // the block spans QPB quarters
+              constexpr int QPB = BK / 32;
+              mine = k == cq / QPB;
+              m = -INFINITY;
+#pragma unroll
+              for (int i = 0; i < QPB; ++i) {
+                const int q = k * QPB + i;
+                m = fmaxf(m, q == cq ? pm[0] : xmax_s[par][((qtr * 4 + q) * 2) * 32 + lane]);
+              }
             }
             const bool on = block_begin(key_t + k * BK);
             if (on) row.run_max = fmaxf(row.run_max, m);
@@ -468,45 +477,6 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         mbar_arrive(&bars.quad[qtr]);
         if (mbar_wait(&bars.quad[qtr], n_done & 1)) append_prev((n_done - 1) & 1);
         else timed_out = true;
-      }
-    } else if (cq == 0) {
-      // k_local_size 128: the block is the whole tile and its maximum is needed before any keep
-      // test, so the tile is read twice (maximum pass, then keep pass) by one thread per row
-      for (int t = t_lo; t < t_hi; ++t) {
-        const int n = t - t_lo, sb = n & 1, ub = n >> 1;
-        if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
-        tc_fence_after();
-        const uint32_t t_s = tmem + (uint32_t)sb * 128 + lane_base;
-        const int key0 = t * kTile;
-        if (block_begin(key0)) {
-          float bmax = -INFINITY;
-#pragma unroll 1
-          for (int c0 = 0; c0 < BK; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(t_s + c0, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (key0 + c0 + j < p.sk) bmax = fmaxf(bmax, __uint_as_float(v[j]));
-          }
-          row.run_max = fmaxf(row.run_max, bmax);
-#pragma unroll 1
-          for (int c0 = 0; c0 < BK; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(t_s + c0, v);
-            tmem_wait_ld();
-            const int kk = key0 + c0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (kk + j < row.hi && __fadd_rn(__uint_as_float(v[j]), row.gap) >= row.run_max) {
-                if (row.cnt < p.capacity) row.out[row.cnt] = kk + j;
-                ++row.cnt;
-              }
-            }
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(&bars.sempty[sb]);
       }
     }
     if (row_ok && !timed_out && cq == 0) {  // the row's count is written by the thread of the first quarter
