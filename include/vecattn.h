@@ -150,12 +150,19 @@ int va_block_tables(int32_t batch, int32_t heads, int32_t seq_len, int32_t pq, i
  * q_pooling_size, k_local_size, group_k_block, causal, chunk_size),
  * spattn/src/VecAttention.py:10-123: pooling, selection and sparse attention for every chunk,
  * enqueued on one stream with no host synchronisation.  workspace must hold
- * va_prefill_workspace_bytes() bytes and be 256-byte aligned.  When the selected-column lists of the
- * whole sequence fit in VA_SINGLE_PASS_INDEX_BYTES, all chunks are processed by one launch per stage
- * (same results: chunk_size then only positions the reference's causal chunk-boundary effect);
- * otherwise chunk_size bounds the workspace exactly as in the reference.  col_count_out (optional,
- * (B,H,ceil(Sq/pq)) int32) receives the per-tile selection counts. */
-#define VA_SINGLE_PASS_INDEX_BYTES (32ull << 30)
+ * va_prefill_workspace_bytes() bytes and be 256-byte aligned.
+ *
+ * Workspace size and chunk_size.  The reference processes chunk_size query rows at a time, which
+ * bounds its index buffer (spattn/src/VecAttention.py:94-108).  Here the caller chooses through
+ * single_pass_budget: when the selected-column lists of the whole sequence
+ * (4 * batch * heads * ceil(Sq/q_pooling_size) * Sk bytes) fit in that many bytes, every stage runs
+ * once for all chunks (same results: chunk_size then only positions the reference's causal
+ * chunk-boundary effect); otherwise the chunk loop of the reference is used and chunk_size bounds
+ * the workspace exactly as it does there.  single_pass_budget = 0 selects
+ * VA_SINGLE_PASS_INDEX_BYTES_DEFAULT; 1 forces the chunk loop.  va_prefill_workspace_bytes and
+ * va_prefill must be given the same value.  col_count_out (optional, (B,H,ceil(Sq/pq)) int32)
+ * receives the per-tile selection counts. */
+#define VA_SINGLE_PASS_INDEX_BYTES_DEFAULT (4ull << 30)
 typedef struct {
   int32_t dtype, batch, heads, kv_heads, sq, sk, head_dim;
   int32_t pq, bk, group_k_block, causal, chunk_size, compat_bsq;
@@ -168,6 +175,7 @@ typedef struct {
   size_t workspace_bytes;
   int32_t* col_count_out;
   int32_t* status;
+  size_t single_pass_budget; /* see above; 0 = VA_SINGLE_PASS_INDEX_BYTES_DEFAULT */
 } va_prefill_args;
 int va_prefill_workspace_bytes(const va_prefill_args* args, size_t* bytes);
 int va_prefill(const va_prefill_args* args, va_stream_t stream);
@@ -181,16 +189,23 @@ int va_prefill(const va_prefill_args* args, va_stream_t stream);
  * thread that is not allowed to touch the allocator's lock.  Such a caller still owns q, k, v and
  * out; what it cannot provide is the scratch va_prefill wants in `workspace`.
  *
- * Same arguments and results as va_prefill; `workspace` and `workspace_bytes` are ignored.  The
- * scratch is a fixed array of VA_STATIC_SCRATCH_BYTES bytes that is part of the library image:
- * every GPU that loads the library carries it until the process exits.  A problem whose scratch
- * (va_prefill_workspace_bytes) exceeds it is refused with VA_ERR_STATIC_SCRATCH and nothing is
- * launched; the scratch is dominated by 4 * batch * heads * ceil(chunk_size / q_pooling_size) * Sk
- * bytes of index lists, so a smaller chunk_size makes a larger problem fit.
+ * Same arguments and results as va_prefill; `workspace`, `workspace_bytes` and `single_pass_budget`
+ * are ignored.  The scratch is a fixed array of VA_STATIC_SCRATCH_BYTES bytes that is part of the
+ * library image: every GPU that loads the library carries it until the process exits.  The whole
+ * sequence is processed in one pass if its scratch fits the array, else chunk by chunk as the
+ * reference does; only a problem whose per-chunk scratch still exceeds the array is refused with
+ * VA_ERR_STATIC_SCRATCH, and then nothing is launched.  (So a problem may be accepted although
+ * va_prefill_workspace_bytes reports more than VA_STATIC_SCRATCH_BYTES for it.)  The per-chunk
+ * scratch is dominated by 4 * batch * heads * ceil(chunk_size / q_pooling_size) * Sk bytes of index
+ * lists, so a smaller chunk_size makes a larger problem fit.  va_prefill_static_fits answers the
+ * question on the host without launching anything (1 = accepted, 0 = refused, negative = the
+ * arguments are invalid).
  *
  * The function calls no cudaMalloc/cudaFree and no allocating library routine.  Its first call on
- * a device looks up the array's device address (cudaGetSymbolAddress, with that device current);
- * make that first call before any stream capture begins.
+ * a device makes the CUDA runtime load the library's device code there, and every call looks up
+ * the array's device address (cudaGetSymbolAddress, with the caller's device current: a host-side
+ * table lookup once the code is loaded); make the first call on a device before any stream capture
+ * begins.
  *
  * All calls on a device share the one array and it keeps whatever the previous call left.  The
  * kernels never read scratch they have not written in the same call, so nothing needs clearing;
@@ -198,6 +213,18 @@ int va_prefill(const va_prefill_args* args, va_stream_t stream);
  * race on it and corrupt each other's results.  Order such calls, or use va_prefill. */
 #define VA_STATIC_SCRATCH_BYTES (32u << 20)
 int va_prefill_static(const va_prefill_args* args, va_stream_t stream);
+int va_prefill_static_fits(const va_prefill_args* args);
+
+/* ---- self-test of the bounded waits -----------------------------------------------------------
+ * No counterpart in the reference.  Every wait inside the kernels (on an mbarrier that a copy, an
+ * MMA or another warp completes) gives up after a fixed number of polls, reports
+ * VA_STATUS_TIMEOUT through the status word and lets the CTA unwind (free its tensor memory,
+ * return), so a protocol bug ends a kernel instead of hanging the GPU.  This entry point runs that
+ * path on purpose: a one-CTA kernel allocates tensor memory, then one of its threads waits with
+ * the kernels' own wait routine, limited to `polls` polls (a few microseconds each), on a barrier
+ * that nothing ever completes.  The kernel returns normally; *status (a device int32, required)
+ * has VA_STATUS_TIMEOUT OR-ed in.  polls must be in [1, 4096]. */
+int va_selftest_wait_timeout(int32_t* status, int32_t polls, va_stream_t stream);
 
 const char* va_status_string(int code);
 int va_version(void);

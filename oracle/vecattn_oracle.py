@@ -126,8 +126,8 @@ def scaled_pooled_q(avg_q: torch.Tensor, scale_in_dtype: bool = False) -> torch.
 
 
 def row_key_limits(nq: int, tile_offset: int, sk: int, pq: int, bk: int, causal: bool,
-                   wo_initial: bool, bsq: int = DEFAULT_BSQ, compat_q1: bool = True
-                   ) -> Tuple[int, np.ndarray]:
+                   wo_initial: bool, bsq: int = DEFAULT_BSQ, compat_q1: bool = True,
+                   rows: Optional[Sequence[int]] = None) -> Tuple[int, np.ndarray]:
     """Eligible key range [lo, hi[r]) of every pooled row of one chunk.
 
     spattn/src/kernels/vecattention_kernels.py:231-233,260.  ``lo``: with ``wo_init`` the
@@ -136,15 +136,18 @@ def row_key_limits(nq: int, tile_offset: int, sk: int, pq: int, bk: int, causal:
     test with a truncating integer division relative to the first tile of the Triton
     program (``bsq`` pooled rows per program), which for the first row of each program
     also drops the key blocks starting inside the preceding tile, except its first one
-    (``compat_q1``).
+    (``compat_q1``).  ``rows`` (optional) gives the position inside the chunk of each of the
+    ``nq`` pooled rows when only a sample of the chunk's rows is evaluated.
     """
     lo = pq if wo_initial else 0
-    g = tile_offset + np.arange(nq, dtype=np.int64)
+    pos = np.arange(nq, dtype=np.int64) if rows is None else np.asarray(rows, dtype=np.int64)
+    assert pos.shape == (nq,)
+    g = tile_offset + pos
     if not causal:
         return lo, np.full(nq, sk, dtype=np.int64)
     hi = np.minimum(sk, g * pq)
     if compat_q1:
-        first = (np.arange(nq) % bsq) == 0
+        first = (pos % bsq) == 0
         hi = np.where(first, np.minimum(hi, (g - 1) * pq + bk), hi)
     return lo, np.maximum(hi, 0)
 
@@ -154,7 +157,7 @@ def select_columns(avg_q: torch.Tensor, k: torch.Tensor, tile_offset: int,
                    wo_initial: bool = False, group_k_block: int = 1,
                    bsq: int = DEFAULT_BSQ, compat_q1: bool = True,
                    return_ambiguous: bool = False, rel_tol: float = 1e-6,
-                   scale_in_dtype: bool = False):
+                   scale_in_dtype: bool = False, rows: Optional[Sequence[int]] = None):
     """Streaming MinP selection.  Restates ``fuse_qk_softmax_minp_wo_causal``
     (spattn/src/kernels/vecattention_kernels.py:59-181) and its Triton kernels (:206-345).
 
@@ -167,7 +170,9 @@ def select_columns(avg_q: torch.Tensor, k: torch.Tensor, tile_offset: int,
     indices ascending (the reference's cross-group order depends on atomics; compare as
     sets).  With ``return_ambiguous`` also returns a list-of-lists of int64 arrays holding,
     per (b,h,row), the keys whose estimate lies within ``rel_tol`` (relative to the
-    magnitudes compared) of the keep/drop boundary in fp64 arithmetic.
+    magnitudes compared) of the keep/drop boundary in fp64 arithmetic.  ``rows``: the pooled
+    rows given are a sample of the chunk's rows, at these positions inside the chunk (the
+    rule is per row; the position only enters the causal key limit).
     """
     b_, h_, nq, d = avg_q.shape
     hkv = k.shape[1]
@@ -180,7 +185,7 @@ def select_columns(avg_q: torch.Tensor, k: torch.Tensor, tile_offset: int,
     if causal and pq % bk != 0:  # vecattention_kernels.py:129
         raise AssertionError("causal requires q_pooling_size % k_local_size == 0")
     qt = scaled_pooled_q(avg_q, scale_in_dtype)
-    lo, hi = row_key_limits(nq, tile_offset, sk, pq, bk, causal, wo_initial, bsq, compat_q1)
+    lo, hi = row_key_limits(nq, tile_offset, sk, pq, bk, causal, wo_initial, bsq, compat_q1, rows)
     hi_t = torch.from_numpy(hi).view(nq, 1)
     nblk = math.ceil(sk / bk)
     ngrp = math.ceil(nblk / g_)
@@ -245,7 +250,8 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pq: int,
                      col_count: torch.Tensor, col_idx: torch.Tensor,
                      causal: bool, q_offset: int = 0, round_p: bool = False,
                      out_dtype: Optional[torch.dtype] = None,
-                     compute_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                     compute_dtype: torch.dtype = torch.float32,
+                     tiles: Optional[Sequence[int]] = None) -> torch.Tensor:
     """softmax(Q K_t^T / sqrt(D)) V_t per query tile over K_t = dense 64-key blocks at
     ``blk_idx[..., :blk_count]`` plus single keys ``col_idx[..., :col_count]``.
 
@@ -256,7 +262,8 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pq: int,
     applied).  ``q`` is (B,H,Sq,D) holding query rows ``q_offset ..``; ``k``/``v`` are
     (B,Hkv,Sk,D).  A tile with no key at all yields zeros (undefined in the reference).
     ``round_p`` rounds the unnormalised probabilities to the input dtype before the PV
-    product, as flash-attention kernels do.
+    product, as flash-attention kernels do.  ``tiles`` restricts the work to these query
+    tiles (the other rows of the result stay zero).
     """
     b_, h_, sq, d = q.shape
     hkv = k.shape[1]
@@ -270,7 +277,7 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pq: int,
         for h in range(h_):
             kh = k[b, h // rep].to(compute_dtype)
             vh = v[b, h // rep].to(compute_dtype)
-            for t in range(nq):
+            for t in (range(nq) if tiles is None else tiles):
                 r0, r1 = t * pq, min((t + 1) * pq, sq)
                 member = torch.zeros(sk, dtype=torch.bool)
                 for off in blk_idx[b, h, t, : int(blk_count[b, h, t])].tolist():

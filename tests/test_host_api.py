@@ -24,7 +24,7 @@ def test_header_symbols_are_exported(lib):
     handle = lib.lib()
     for name in declared:
         assert hasattr(handle, name)
-    assert handle.va_version() >= 100
+    assert handle.va_version() >= 200
     assert lib.status_string(0) == "ok"
     for code in range(-8, 0):
         assert "unknown" not in lib.status_string(code)
@@ -37,7 +37,7 @@ def test_struct_layout_matches_header(lib):
     assert C.sizeof(lib.PoolArgs) == 24 + 32 + 8
     assert C.sizeof(lib.SelectArgs) == 56 + 8 + 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8
     assert C.sizeof(lib.AttnArgs) == 40 + 4 * 32 + 8 * 6 + 8 + 8 + 8
-    assert C.sizeof(lib.PrefillArgs) == 56 + 4 * 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8
+    assert C.sizeof(lib.PrefillArgs) == 56 + 4 * 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8
 
 
 def test_validation_returns_codes_without_launching(lib):
@@ -98,8 +98,18 @@ def test_prefill_workspace_bytes(lib):
     small = C.c_size_t(0)
     assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(small)) == 0
     assert small.value < big.value / 3.9
+    # the budget belongs to the caller: the quick-use shape (2 GiB of index lists) goes through the chunk
+    # loop once the budget is below that, and the workspace then shrinks with chunk_size
     a.heads = a.kv_heads = 32
     a.sq = a.sk = 32768
+    sizes = []
+    for budget, chunk in [(0, 8192), (1 << 30, 32768), (1 << 30, 8192), (1, 4096)]:
+        a.single_pass_budget, a.chunk_size = budget, chunk
+        assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n2)) == 0
+        sizes.append(n2.value)
+    assert sizes[0] == n.value and sizes[1] == n.value      # one chunk covers the sequence
+    assert sizes[2] < n.value / 3.9 and sizes[3] < n.value / 7.8
+    a.single_pass_budget = 0
     a.chunk_size = 100
     assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n2)) == -7
     a.chunk_size, a.causal, a.sk = 8192, 1, 4096
@@ -209,3 +219,23 @@ def test_stage_workspace_queries_report_no_scratch(lib):
     n = C.c_size_t(123)
     assert lib.lib().va_sparse_attn_workspace_bytes(C.byref(lib.AttnArgs()), C.byref(n)) == 0 and n.value == 0
     assert lib.lib().va_select_workspace_bytes(None, C.byref(n)) == -1
+
+
+def test_wait_selftest_and_static_fit_validate_their_arguments(lib):
+    h = lib.lib()
+    assert h.va_selftest_wait_timeout(None, 10, None) == -1
+    assert h.va_selftest_wait_timeout(16, 0, None) == -3
+    assert h.va_selftest_wait_timeout(16, 5000, None) == -3
+    a = lib.PrefillArgs()
+    a.dtype, a.batch, a.heads, a.kv_heads, a.sq, a.sk, a.head_dim = 0, 1, 32, 32, 32768, 32768, 128
+    a.pq, a.bk, a.group_k_block, a.causal, a.chunk_size, a.compat_bsq = 64, 16, 16, 0, 32768, 64
+    assert h.va_prefill_static_fits(C.byref(a)) == 0          # 2 GiB of index lists per chunk
+    a.heads = a.kv_heads = 4
+    a.sq = a.sk = 12288
+    a.chunk_size = 1024                                        # fits chunk by chunk, not in one pass
+    n = C.c_size_t(0)
+    assert h.va_prefill_workspace_bytes(C.byref(a), C.byref(n)) == 0 and n.value > lib.VA_STATIC_SCRATCH_BYTES
+    assert h.va_prefill_static_fits(C.byref(a)) == 1
+    a.chunk_size = 100
+    assert h.va_prefill_static_fits(C.byref(a)) == -7
+    assert h.va_prefill_static_fits(None) == -1

@@ -19,7 +19,7 @@ def _args(L, q, k, v, out, causal, chunk, counts=None):
     t4 = lambda t: L.Tensor4(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
     return L.PrefillArgs(L.VA_BF16, b, h, k.shape[1], s, k.shape[2], d, 64, 16, 16, int(causal), chunk, 64,
                          t4(q), t4(k), t4(v), t4(out), 0.6931, None, 0, None, 0,
-                         counts.data_ptr() if counts is not None else None, None)
+                         counts.data_ptr() if counts is not None else None, None, 0)
 
 
 def test_static_scratch_limit_is_enforced_before_any_launch(built_library):

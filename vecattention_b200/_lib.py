@@ -16,8 +16,9 @@ VA_STATUS_TIMEOUT = 2
 
 # every symbol include/vecattn.h declares
 EXPORTS = ("va_pool_q", "va_select", "va_select_workspace_bytes", "va_sparse_attn", "va_sparse_attn_workspace_bytes",
-           "va_block_tables", "va_prefill_workspace_bytes", "va_prefill", "va_prefill_static", "va_status_string",
-           "va_version")
+           "va_block_tables", "va_prefill_workspace_bytes", "va_prefill", "va_prefill_static", "va_prefill_static_fits",
+           "va_selftest_wait_timeout", "va_status_string", "va_version")
+VA_SINGLE_PASS_INDEX_BYTES_DEFAULT = 4 << 30
 VA_STATIC_SCRATCH_BYTES = 32 << 20
 
 
@@ -59,7 +60,7 @@ class PrefillArgs(C.Structure):
                 ("q", Tensor4), ("k", Tensor4), ("v", Tensor4), ("out", Tensor4),
                 ("gap", C.c_float), ("gaps", C.c_void_p), ("gaps_stride_b", C.c_int64),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("col_count_out", C.c_void_p), ("status", C.c_void_p)]
+                ("col_count_out", C.c_void_p), ("status", C.c_void_p), ("single_pass_budget", C.c_size_t)]
 
 
 _LIB = None
@@ -87,6 +88,8 @@ def lib() -> C.CDLL:
     handle.va_prefill_workspace_bytes.argtypes = [C.POINTER(PrefillArgs), C.POINTER(C.c_size_t)]
     handle.va_prefill.argtypes = [C.POINTER(PrefillArgs), C.c_void_p]
     handle.va_prefill_static.argtypes = [C.POINTER(PrefillArgs), C.c_void_p]
+    handle.va_prefill_static_fits.argtypes = [C.POINTER(PrefillArgs)]
+    handle.va_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
     for name in EXPORTS:
         getattr(handle, name).restype = C.c_int
     handle.va_status_string.argtypes = [C.c_int]

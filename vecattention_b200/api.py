@@ -228,6 +228,7 @@ def VecAttention_prefill(
     return_selection: bool = False,
     out: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
+    single_pass_budget: Optional[int] = None,
 ):
     """Vectorized sparse attention prefill (VecAttention) on B200.
 
@@ -245,6 +246,12 @@ def VecAttention_prefill(
         out: preallocated output
         status: int32 device tensor of one element that receives VA_STATUS_* bits (index capacity
             overflow, internal wait timeout); not cleared here, not read back here
+        single_pass_budget: bytes of selected-column lists up to which the whole sequence is
+            processed by one launch per stage instead of the reference's chunk loop (same
+            results).  ``None`` picks it from the memory that is free right now (at most 40 % of
+            it, at most 32 GiB); ``1`` forces the chunk loop, where ``chunk_size`` bounds the
+            workspace as it does in the reference.  If the workspace cannot be allocated the
+            call is retried with the chunk loop.
 
     Returns:
         attn_output: (batch, num_heads, seq_len, head_dim)
@@ -282,10 +289,21 @@ def VecAttention_prefill(
                          _t4(q), _t4(k), _t4(v), _t4(out), gapf,
                          gaps.data_ptr() if gaps is not None else None, gstride, None, 0,
                          counts.data_ptr() if counts is not None else None,
-                         status.data_ptr() if status is not None else None)
+                         status.data_ptr() if status is not None else None, 0)
+    if single_pass_budget is None:
+        free, _ = torch.cuda.mem_get_info(dev)
+        single_pass_budget = max(1, min(32 << 30, int(free * 0.4)))
+    args.single_pass_budget = int(single_pass_budget)
     nbytes = C.c_size_t(0)
     _check(L.lib().va_prefill_workspace_bytes(C.byref(args), C.byref(nbytes)))
-    ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+    try:
+        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+    except torch.cuda.OutOfMemoryError:
+        if args.single_pass_budget == 1:
+            raise
+        args.single_pass_budget = 1  # the reference's chunk loop: chunk_size bounds the workspace
+        _check(L.lib().va_prefill_workspace_bytes(C.byref(args), C.byref(nbytes)))
+        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
     args.workspace = ws.data_ptr()
     args.workspace_bytes = nbytes.value
     with torch.cuda.device(dev):

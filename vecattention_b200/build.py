@@ -15,7 +15,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libvecattn.so")
 SOURCES = ["va_api.cu", "va_pool.cu", "va_select.cu", "va_attn.cu", "va_attn64.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC"] + os.environ.get("VA_EXTRA_NVCC_FLAGS", "").split()
+              "-Xcompiler", "-fPIC"]
 
 
 def _nvcc() -> str:

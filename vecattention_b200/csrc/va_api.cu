@@ -1,6 +1,7 @@
 // C ABI of libvecattn.so: argument validation, workspace carving and kernel launches.
 // No device allocation, no host synchronisation, no C++ exception crosses this boundary.
 #include "va_common.cuh"
+#include "va_sm100.cuh"
 
 namespace va {
 int pool_q(const va_pool_args& a, cudaStream_t stream);
@@ -48,7 +49,11 @@ struct PrefillPlan {
   size_t off_avg, off_cnt, off_idx, off_bcnt, off_bidx, total;
 };
 
-static int plan_prefill(const va_prefill_args& a, PrefillPlan& pl, size_t single_pass_budget = VA_SINGLE_PASS_INDEX_BYTES) {
+static inline size_t budget_of(const va_prefill_args& a) {
+  return a.single_pass_budget ? a.single_pass_budget : (size_t)VA_SINGLE_PASS_INDEX_BYTES_DEFAULT;
+}
+
+static int plan_prefill(const va_prefill_args& a, PrefillPlan& pl, size_t single_pass_budget) {
   if (a.dtype != VA_BF16 && a.dtype != VA_FP16) return VA_ERR_DTYPE;
   if (a.head_dim != kHeadDim || a.batch <= 0 || a.heads <= 0 || a.kv_heads <= 0 || a.sq <= 0 || a.sk <= 0)
     return VA_ERR_SHAPE;
@@ -82,7 +87,7 @@ using namespace va;
 
 extern "C" {
 
-int va_version(void) { return 100; }
+int va_version(void) { return 200; }
 
 const char* va_status_string(int code) {
   switch (code) {
@@ -169,7 +174,7 @@ int va_block_tables(int32_t batch, int32_t heads, int32_t seq_len, int32_t pq, i
 int va_prefill_workspace_bytes(const va_prefill_args* a, size_t* bytes) {
   if (!a || !bytes) return VA_ERR_NULL;
   PrefillPlan pl;
-  if (int rc = plan_prefill(*a, pl)) return rc;
+  if (int rc = plan_prefill(*a, pl, budget_of(*a))) return rc;
   *bytes = pl.total;
   return VA_OK;
 }
@@ -242,7 +247,10 @@ static int run_prefill(const va_prefill_args* a, size_t single_pass_budget, va_s
   return VA_OK;
 }
 
-int va_prefill(const va_prefill_args* a, va_stream_t stream) { return run_prefill(a, VA_SINGLE_PASS_INDEX_BYTES, stream); }
+int va_prefill(const va_prefill_args* a, va_stream_t stream) {
+  if (!a) return VA_ERR_NULL;
+  return run_prefill(a, budget_of(*a), stream);
+}
 
 // ---- the operator for callers that cannot allocate device memory -----------------------------
 // The scratch of the prefill (pooled queries, per-tile counts, block tables and the selected-
@@ -250,32 +258,77 @@ int va_prefill(const va_prefill_args* a, va_stream_t stream) { return run_prefil
 // part of the loaded module, so every GPU that loads the library holds it until the process exits.
 static __device__ __align__(256) unsigned char g_static_scratch[VA_STATIC_SCRATCH_BYTES];
 
-int va_prefill_static(const va_prefill_args* a, va_stream_t stream) {
-  if (!a) return VA_ERR_NULL;
-  // one pass over the whole sequence if that fits the array, else chunk by chunk
-  size_t budget = VA_STATIC_SCRATCH_BYTES;
-  PrefillPlan pl;
-  if (int rc = plan_prefill(*a, pl, budget)) return rc;
+// One pass over the whole sequence if that fits the array, else chunk by chunk; VA_ERR_STATIC_SCRATCH
+// if even one chunk's scratch exceeds it.  `budget` receives the single-pass budget of the chosen plan.
+static int plan_static(const va_prefill_args& a, PrefillPlan& pl, size_t& budget) {
+  budget = VA_STATIC_SCRATCH_BYTES;
+  if (int rc = plan_prefill(a, pl, budget)) return rc;
   if (pl.total > (size_t)VA_STATIC_SCRATCH_BYTES) {
-    budget = 0;
-    if (int rc = plan_prefill(*a, pl, budget)) return rc;
+    budget = 1;  // nothing fits one byte: the chunk loop
+    if (int rc = plan_prefill(a, pl, budget)) return rc;
     if (pl.total > (size_t)VA_STATIC_SCRATCH_BYTES) return VA_ERR_STATIC_SCRATCH;
   }
+  return VA_OK;
+}
+
+int va_prefill_static_fits(const va_prefill_args* a) {
+  if (!a) return VA_ERR_NULL;
+  PrefillPlan pl;
+  size_t budget;
+  const int rc = plan_static(*a, pl, budget);
+  return rc == VA_OK ? 1 : (rc == VA_ERR_STATIC_SCRATCH ? 0 : rc);
+}
+
+int va_prefill_static(const va_prefill_args* a, va_stream_t stream) {
+  if (!a) return VA_ERR_NULL;
+  PrefillPlan pl;
+  size_t budget;
+  if (int rc = plan_static(*a, pl, budget)) return rc;
   // In host code `g_static_scratch` names a host-side shadow of the array, not device memory: the
-  // device address must be asked for, once per device, with that device current.
-  constexpr int kMaxDevices = 64;
-  static void* scratch_of_device[kMaxDevices] = {};
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return VA_ERR_CUDA;
-  void* ptr = __atomic_load_n(&scratch_of_device[dev], __ATOMIC_ACQUIRE);
-  if (!ptr) {
-    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return VA_ERR_CUDA;
-    __atomic_store_n(&scratch_of_device[dev], ptr, __ATOMIC_RELEASE);  // every thread computes the same value
-  }
+  // device address must be asked for, with the caller's device current.  It is asked for on every
+  // call (a host-side lookup once the module is loaded on the device), so nothing stale survives a
+  // cudaDeviceReset or a re-created context.
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return VA_ERR_CUDA;
   va_prefill_args b = *a;
   b.workspace = ptr;
   b.workspace_bytes = VA_STATIC_SCRATCH_BYTES;
   return run_prefill(&b, budget, stream);
+}
+
+// ---- self-test of the bounded waits -----------------------------------------------------------
+// One CTA: warp 0 allocates tensor memory as the real kernels do; one thread of warp 1 waits, with
+// the kernels' own wait routine, on a barrier that nothing completes.  The wait gives up after
+// `polls` polls, the status word receives VA_STATUS_TIMEOUT, the CTA meets at its final barrier and
+// frees the tensor memory: the unwinding path of the real kernels, run on purpose.
+__global__ void __launch_bounds__(64, 1) wait_timeout_kernel(int32_t* status, int polls) {
+  __shared__ uint64_t never;
+  __shared__ uint32_t tmem_base_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    sm100::mbar_init(&never, 1);
+    sm100::fence_proxy_async();
+  }
+  if (warp == 0) {
+    sm100::tmem_alloc(&tmem_base_s, 32);
+    sm100::tmem_relinquish();
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  sm100::tc_fence_after();
+  bool timed_out = false;
+  if (warp == 1 && lane == 0) timed_out = !sm100::mbar_wait(&never, 0, polls);
+  if (timed_out) atomicOr(status, VA_STATUS_TIMEOUT);
+  sm100::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) sm100::tmem_dealloc(tmem_base_s, 32);
+}
+
+int va_selftest_wait_timeout(int32_t* status, int32_t polls, va_stream_t stream) {
+  if (!status) return VA_ERR_NULL;
+  if (polls < 1 || polls > 4096) return VA_ERR_SHAPE;
+  wait_timeout_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status, polls);
+  return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
 }
 
 }  // extern "C"

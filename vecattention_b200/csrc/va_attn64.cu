@@ -35,17 +35,6 @@ using namespace sm100;
 
 namespace {
 
-// Build with -DVA_DEBUG_STAMPS to record clock64() time stamps of one CTA's pipeline events.
-#ifdef VA_DEBUG_STAMPS
-__device__ long long g_stamps[32 * 16];
-__device__ long long g_cta_times[4 * 8192];  // per CTA of head 0: SM id, entry, pipeline start, exit (clock64 of that SM)
-#define VA_CTA_TIME(slot) do { if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 8192) { if ((slot) == 0) { unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); g_cta_times[blockIdx.x * 4] = sm; } g_cta_times[blockIdx.x * 4 + 1 + (slot)] = clock64(); } } while (0)
-#define VA_STAMP(ev, j) do { if (blockIdx.x == 7 && blockIdx.y == 0 && (j) < 16) g_stamps[(ev) * 16 + (j)] = clock64(); } while (0)
-#else
-#define VA_STAMP(ev, j) do { } while (0)
-#define VA_CTA_TIME(slot) do { } while (0)
-#endif
-
 constexpr int kChunk = 128;
 constexpr int kKvTile = 128 * 256;  // 128 gathered rows
 constexpr int kQTile = 64 * 256;    // 64 query rows / 64 rows of P
@@ -94,7 +83,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   __shared__ float fin_s[256];       // [group][TMEM lane]: row sums, added in the epilogue
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  VA_CTA_TIME(0);
   // causal tiles grow with their index: the longest are started first, so the grid's tail is made of short ones
   const int tile = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int hkv = h / p.rep;
@@ -151,7 +139,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  VA_CTA_TIME(1);
   const uint32_t t_s0 = tmem, t_o = tmem + 128;  // S buffers at columns 0 and 64, O at 128 (64 columns each)
 
   bool timed_out = false;
@@ -220,7 +207,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       int keys[16];
       int raw0 = fetch_raw(0), raw1 = nchunks > 1 ? fetch_raw(1) : 0;
       for (int j = 0; j < nchunks && !timed_out; ++j) {
-        if (pt == 0) VA_STAMP(is_v ? 3 : 0, j);
         const int key = decode(j, raw0);
         raw0 = raw1;
         if (j + 2 < nchunks) raw1 = fetch_raw(j + 2);
@@ -235,14 +221,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
         if (!is_v) {
           const int ks = j % kKStages, ku = j / kKStages;
           if (!mbar_wait(&bars.kempty[ks], (ku & 1) ^ 1)) { timed_out = true; break; }
-          if (pt == 0) VA_STAMP(1, j);
           copy_tile(k_s + (size_t)ks * kKvTile, kb, p.k_ss, keys, &bars.kfull[ks]);
-          if (pt == 0) VA_STAMP(2, j);
         } else {
           const int vs = j % kVStages, vu = j / kVStages;
           if (!mbar_wait(&bars.vempty[vs], (vu & 1) ^ 1)) { timed_out = true; break; }
           copy_tile(v_s + (size_t)vs * kKvTile, vb, p.v_ss, keys, &bars.vfull[vs]);
-          if (pt == 0) VA_STAMP(4, j);
         }
       }
     }
@@ -263,8 +246,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
           const int s = j % kKStages, u = j / kKStages, sb = j & 1, ub = j >> 1;
           ok = mbar_wait(&bars.kfull[s], u & 1) && mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1);
           if (!ok) break;
+          fence_proxy_async();  // the producers' cp.async writes (generic proxy) -> visible to the MMA's operand reads
           tc_fence_after();
-          VA_STAMP(5, j);
           const uint32_t k_addr = kr_addr + (uint32_t)s * kKvTile;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
@@ -275,7 +258,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
           }
           umma_commit(&bars.kempty[s]);
           umma_commit(&bars.sfull[sb]);
-          VA_STAMP(6, j);
         }
       } else {
         constexpr uint32_t idesc_pv = umma_idesc(64, 128, in16, 0, 1);
@@ -284,8 +266,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
           const int s = j % kVStages, u = j / kVStages, pb = j & 1, upb = j >> 1;
           ok = mbar_wait(&bars.vfull[s], u & 1) && mbar_wait(&bars.pfull[pb], upb & 1);
           if (!ok) break;
+          fence_proxy_async();
           tc_fence_after();
-          VA_STAMP(7, j);
           const uint32_t v_addr = vr_addr + (uint32_t)s * kKvTile;
           const uint32_t pa = p_addr + (uint32_t)pb * kQTile;
 #pragma unroll
@@ -327,7 +309,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       const int* keys = keys_s[j & 7] + half * 64;
       if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
       tc_fence_after();
-      if (tid == 0) VA_STAMP(8, j);
       const int4 mk = *reinterpret_cast<const int4*>(mask_s[j & 7]);
       const bool masked = (mk.x | mk.y | mk.z | mk.w) != 0;
       // ---- this thread's 64 scores -> registers; the S buffer is free again right away ----
@@ -362,7 +343,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       if (!mbar_wait(&bars.xch[grp * 2 + pair], xc & 1)) { timed_out = true; break; }
       mx = fmaxf(mx, xbuf[(xc & 1) * 128 + (tl ^ 64)]);
       ++xc;
-      if (tid == 0) VA_STAMP(9, j);
       // ---- the row's reference maximum: continue from what the previous chunk (other group) left ----
       if (j > 0 && !mbar_wait(&bars.dec[grp ^ 1], ((j - 1) >> 1) & 1)) { timed_out = true; break; }
       const float m_prev = j > 0 ? m_row_s[(j - 1) & 1][row] : -INFINITY;
@@ -396,7 +376,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
         l *= ex2_approx(m_seen - m_new);
         m_seen = m_new;
       }
-      if (tid == 0) VA_STAMP(10, j);
       const float mref = m_new == -INFINITY ? 0.f : m_new;
       // ---- P = exp2(S * scale - m), row sum, P -> shared memory (K-major operand, this thread's 64 keys) ----
       unsigned char* pdst = p_s + (size_t)sb * kQTile;
@@ -418,7 +397,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       tc_fence_before();
       fence_proxy_async();
       mbar_arrive(&bars.pfull[sb]);
-      if (tid == 0) VA_STAMP(11, j);
     }
     // ---- epilogue: O / l -> global.  Every thread first brings its row sum to the final scale
     // (the last chunk's decision), then the four owners of a row add their sums. ----
@@ -464,7 +442,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   tc_fence_before();
   __syncthreads();
   if (warp == 16) tmem_dealloc(tmem, 256);
-  VA_CTA_TIME(2);
 }
 
 template <int DT>
@@ -480,14 +457,6 @@ int launch(const AttnParams& p, int batch, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef VA_DEBUG_STAMPS
-extern "C" int va_debug_read_stamps(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_stamps, sizeof(long long) * 32 * 16);
-}
-extern "C" int va_debug_read_cta_times(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(long long) * 4 * 8192);
-}
-#endif
 
 int launch_attn64(const AttnParams& p, int dtype, int batch, cudaStream_t stream) {
   return dtype == VA_BF16 ? launch<VA_BF16>(p, batch, stream) : launch<VA_FP16>(p, batch, stream);

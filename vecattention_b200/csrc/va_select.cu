@@ -49,14 +49,6 @@ struct SelectParams {
 
 namespace {
 
-// Build with -DVA_DEBUG_STAMPS to record clock64() time stamps of one CTA's pipeline events.
-#ifdef VA_DEBUG_STAMPS
-__device__ long long g_sel_stamps[16 * 16];
-#define VA_STAMP(ev, j) do { if (blockIdx.x == 1 && blockIdx.y == 0 && (j) >= 8 && (j) < 24) g_sel_stamps[(ev) * 16 + (j) - 8] = clock64(); } while (0)
-#else
-#define VA_STAMP(ev, j) do { } while (0)
-#endif
-
 constexpr int kRows = 128;   // pooled rows per CTA
 constexpr int kTile = 128;   // keys per tile
 constexpr int kTileBytes = 128 * 256;
@@ -254,7 +246,6 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
     for (int t = t_lo; t < t_hi; ++t) {
       const int n = t - t_lo, s = n % kStages, u = n / kStages;
       if (!mbar_wait(&bars.kempty[s], (u & 1) ^ 1)) { timed_out = true; break; }
-      if (tid == 512) VA_STAMP(0, n);
       const uint32_t dst = smem_addr(k_s + (size_t)s * kTileBytes) + dst_off;
       const int key0 = t * kTile + rbase;
       if (t * kTile + kTile <= p.sk) {
@@ -268,7 +259,6 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
       }
       cp_async_arrive_noinc(&bars.kfull[s]);
       mbar_arrive(&bars.kfull[s]);
-      if (tid == 512) VA_STAMP(1, n);
     }
     cp_async_commit();
     cp_async_wait<0>();  // nothing of this thread may still be in flight when the CTA retires
@@ -286,7 +276,6 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         if (!mbar_wait(&bars.kfull[s], u & 1) || !mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1)) { timed_out = true; break; }
         fence_proxy_async();
         tc_fence_after();
-        VA_STAMP(2, n);
         const uint32_t k_addr = kr_addr + (uint32_t)s * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -294,7 +283,6 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
                umma_desc(k_addr + (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32, 16, 1024), idesc, ks > 0);
         umma_commit(&bars.kempty[s]);
         umma_commit(&bars.sfull[sb]);
-        VA_STAMP(3, n);
       }
     }
   } else {
@@ -366,7 +354,6 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         const int n = t - t_lo, sb = n & 1, ub = n >> 1, par = n & 1;
         if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
         tc_fence_after();
-        if (tid == 0) VA_STAMP(4, n);
         const int key_t = t * kTile, key_q = key_t + cq * 32;
         // ---- my 32 estimates -> registers; the accumulator buffer is free again ----
         uint32_t v[32];
@@ -374,7 +361,6 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&bars.sempty[sb]);
-        if (tid == 0) VA_STAMP(5, n);
         // ---- maxima of my key blocks (keys past the sequence end never count) ----
         float pm[NP];
         if (key_q + 32 <= p.sk) {
@@ -392,14 +378,11 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
 #pragma unroll
         for (int kb = 0; kb < NP; ++kb) xmax_s[par][((qtr * 4 + cq) * 2 + kb) * 32 + lane] = pm[kb];
         mbar_arrive(&bars.quad[qtr]);
-        if (tid == 0) VA_STAMP(6, n);
         if (!mbar_wait(&bars.quad[qtr], par)) { timed_out = true; break; }
-        if (tid == 0) VA_STAMP(7, n);
         if (n > 0) {  // the previous tile: where it ended and where its keys go
           row.run_max = xrm_s[par ^ 1][qtr * 32 + lane];
           append_prev(par ^ 1);
         }
-        if (tid == 0) VA_STAMP(9, n);
         // ---- running maximum entering / after every block of the tile, identical in the four threads ----
         // A tile inside the walked key range (all but the first and last of a CTA) needs no range
         // tests and lets each thread stop at its own last block.
@@ -446,7 +429,6 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
           }
         }
         if (cq == 3) xrm_s[par][qtr * 32 + lane] = row.run_max;  // the value the next tile starts from
-        if (tid == 0) VA_STAMP(11, n);
         // ---- keep mask of my 32 keys.  fp32(s + gap) >= m  <=>  the difference fp32(s + gap) - m is
         // not negative (a difference of two floats has the exact sign); its sign bit is shifted
         // into the mask, last key first, so key c ends up in bit c.  Two additions on the FMA pipe
@@ -457,20 +439,17 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
           const float d = __fsub_rn(__fadd_rn(__uint_as_float(v[c]), row.gap), rm_own[c / SB]);
           neg = __funnelshift_l(__float_as_uint(d), neg, 1);
         }
-        if (tid == 0) VA_STAMP(12, n);
         uint32_t mask = ~neg;
 #pragma unroll
         for (int kb = 0; kb < NP; ++kb)
           if (!on_own[kb]) mask &= ~((SB == 32 ? 0xffffffffu : ((1u << SB) - 1u)) << (kb * SB));
         const int room = row.hi - key_q;  // keys at or past the row's limit are cut off
         if (room < 32) mask = room <= 0 ? 0u : (mask & ((1u << room) - 1u));
-        if (tid == 0) VA_STAMP(8, n);
         prev_mask = mask;
         prev_key = key_q;
         prev_cnt = __popc(mask);
         xcnt_s[par][(qtr * 4 + cq) * 32 + lane] = prev_cnt;
         n_done = n + 1;
-        if (tid == 0) VA_STAMP(10, n);
       }
       // ---- the last tile's keys: one more meeting for its counts ----
       if (!timed_out && n_done > 0) {
@@ -514,11 +493,6 @@ int launch_dt(const SelectParams& p, int bk, int batch, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef VA_DEBUG_STAMPS
-extern "C" int va_debug_read_select_stamps(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_sel_stamps, sizeof(long long) * 16 * 16);
-}
-#endif
 
 int select(const va_select_args& a, cudaStream_t stream) {
   SelectParams p;

@@ -39,9 +39,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // caller records an error and leaves its loop, so a protocol bug ends the kernel instead of
 // hanging the GPU.
 constexpr int kWaitLimit = 1 << 18;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit = kWaitLimit) {
 #pragma unroll 1  // unrolled, every wait site would carry dozens of copies of the poll
-  for (int i = 0; i < kWaitLimit; ++i)
+  for (int i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
