@@ -81,6 +81,11 @@ int va_pool_q(const va_pool_args* args, va_stream_t stream);
  *              (truncating division at :260).  0 = strict rule (all keys before the diagonal tile).
  *   col_count  (B,H,nq) int32 out; col_idx (B,H,nq,capacity) int32 out, every row ascending.
  *              capacity >= Sk can never overflow.  status (optional) receives VA_STATUS_* bits.
+ *   workspace  scratch of va_select_workspace_bytes() bytes, 16-byte aligned: one keep bit per
+ *              (pooled row, key), written by the estimate kernel and read by the kernel that forms
+ *              the index lists (about Sk / 8 bytes per pooled row; the reference's wrapper allocates
+ *              a zero-filled (B,H,nq,Sk) int32 buffer and a padded copy of K instead,
+ *              vecattention_kernels.py:104-136).
  * Unlike the reference no buffer is zero-filled: entries of col_idx past col_count are not written. */
 typedef struct {
   int32_t dtype, batch, heads, kv_heads, nq, sk, head_dim;
@@ -97,11 +102,11 @@ typedef struct {
   int32_t* status;
   int32_t chunk_tiles; /* > 0: avg_q spans several prefill chunks of chunk_tiles query tiles each and the
                           compat_bsq rule restarts at every chunk boundary; 0: avg_q is one chunk */
+  void* workspace;
+  size_t workspace_bytes;
 } va_select_args;
 int va_select(const va_select_args* args, va_stream_t stream);
-/* Scratch va_select needs besides its outputs: none (bytes = 0).  Present so that a binding written
- * against a workspace-query convention has something to call; the reference's wrapper allocates a
- * zero-filled index buffer and a padded K copy per call (vecattention_kernels.py:104-136). */
+/* Bytes of scratch va_select needs for these sizes (batch, heads, kv_heads, nq, sk are read). */
 int va_select_workspace_bytes(const va_select_args* args, size_t* bytes);
 
 /* ---- vector-sparse flash attention --------------------------------------------------------------

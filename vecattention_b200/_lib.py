@@ -39,7 +39,8 @@ class SelectArgs(C.Structure):
                 ("tile_offset", C.c_int32),
                 ("avg_q", C.c_void_p), ("k", Tensor4), ("gap", C.c_float), ("gaps", C.c_void_p),
                 ("gaps_stride_b", C.c_int64), ("col_count", C.c_void_p), ("col_idx", C.c_void_p),
-                ("capacity", C.c_int64), ("status", C.c_void_p), ("chunk_tiles", C.c_int32)]
+                ("capacity", C.c_int64), ("status", C.c_void_p), ("chunk_tiles", C.c_int32),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
 class AttnArgs(C.Structure):

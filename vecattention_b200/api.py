@@ -130,9 +130,13 @@ def fuse_qk_softmax_minp_wo_causal(avg_q_chunk: torch.Tensor, k: torch.Tensor, a
                         int(avg_q_chunk_offset), avg_q_chunk.data_ptr(), _t4(k), gapf,
                         gaps.data_ptr() if gaps is not None else None, gstride,
                         count.data_ptr(), index.data_ptr(), cap,
-                        status.data_ptr() if status is not None else None)
+                        status.data_ptr() if status is not None else None, 0, None, 0)
     if avg_q_chunk.dtype != k.dtype:
         raise VecAttentionArgumentError("pooled queries and keys must have the same dtype")
+    nbytes = C.c_size_t(0)
+    _check(L.lib().va_select_workspace_bytes(C.byref(args), C.byref(nbytes)))
+    ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)  # keep bits, one per (pooled row, key)
+    args.workspace, args.workspace_bytes = ws.data_ptr(), nbytes.value
     with torch.cuda.device(dev):
         _check(L.lib().va_select(C.byref(args), _stream()))
     if trim:

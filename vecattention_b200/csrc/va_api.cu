@@ -6,6 +6,7 @@
 namespace va {
 int pool_q(const va_pool_args& a, cudaStream_t stream);
 int select(const va_select_args& a, cudaStream_t stream);
+size_t select_workspace_bytes(int batch, int heads, int kv_heads, int nq, int sk);
 int sparse_attn(const va_attn_args& a, cudaStream_t stream);
 
 // dense-block tables of query tiles [tile_off, tile_off + nqc) written as a contiguous (BH, nqc) slice
@@ -46,7 +47,7 @@ static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; 
 struct PrefillPlan {
   int nq_total, nqc_max, blk_width, step;  // step: query rows handled per launch
   int64_t capacity;
-  size_t off_avg, off_cnt, off_idx, off_bcnt, off_bidx, total;
+  size_t off_avg, off_cnt, off_idx, off_bcnt, off_bidx, off_mask, mask_bytes, total;
 };
 
 static inline size_t budget_of(const va_prefill_args& a) {
@@ -77,6 +78,8 @@ static int plan_prefill(const va_prefill_args& a, PrefillPlan& pl, size_t single
   pl.off_cnt = off;  off = align_up(off + bh * pl.nqc_max * 4, 256);
   pl.off_bcnt = off; off = align_up(off + bh * pl.nqc_max * 4, 256);
   pl.off_bidx = off; off = align_up(off + bh * pl.nqc_max * pl.blk_width * 4, 256);
+  pl.mask_bytes = select_workspace_bytes(a.batch, a.heads, a.kv_heads, pl.nqc_max, a.sk);
+  pl.off_mask = off; off = align_up(off + pl.mask_bytes, 256);
   pl.off_idx = off;  off = align_up(off + bh * pl.nqc_max * (size_t)pl.capacity * 4, 256);
   pl.total = off;
   return VA_OK;
@@ -132,7 +135,9 @@ int va_select(const va_select_args* a, va_stream_t stream) {
 
 int va_select_workspace_bytes(const va_select_args* a, size_t* bytes) {
   if (!a || !bytes) return VA_ERR_NULL;
-  *bytes = 0;  // the kernel keeps its state in registers, shared and tensor memory
+  if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->nq <= 0 || a->sk <= 0 || a->heads % a->kv_heads != 0)
+    return VA_ERR_SHAPE;
+  *bytes = select_workspace_bytes(a->batch, a->heads, a->kv_heads, a->nq, a->sk);
   return VA_OK;
 }
 
@@ -219,6 +224,7 @@ static int run_prefill(const va_prefill_args* a, size_t single_pass_budget, va_s
     sa.avg_q = avg; sa.k = a->k; sa.gap = a->gap; sa.gaps = a->gaps; sa.gaps_stride_b = a->gaps_stride_b;
     sa.col_count = cnt; sa.col_idx = idx; sa.capacity = pl.capacity; sa.status = a->status;
     sa.chunk_tiles = a->chunk_size / a->pq;
+    sa.workspace = ws + pl.off_mask; sa.workspace_bytes = pl.mask_bytes;
     if (int rc = select(sa, stream)) return rc;
 
     block_tables_kernel<<<(bh * nqc + 255) / 256, 256, 0, stream>>>(bh, a->sq, a->pq, a->causal, i / a->pq, nqc, bcnt,

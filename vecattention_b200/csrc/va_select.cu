@@ -1,31 +1,33 @@
 // Important-vector selection: pooled-Q . K^T estimate + streaming MinP threshold + compaction,
 // with the estimate on tcgen05 tensor cores and the accumulator in tensor memory.
 //
-// Work decomposition.  The pooled rows of all query heads that share one KV head form one row
-// list (row R -> head hkv*rep + R/nq, tile R%nq); a CTA owns 128 consecutive rows of that list and
-// walks the keys of its KV head once, 128 keys per tile, in ascending order.  Because one CTA sees
-// all keys of its rows in order, the running (prefix) maximum of a key-block group is a per-thread
-// register, every row's index list comes out ascending and deterministic, and no atomics, no
-// zero-filled buffers and no second pass are needed.
+// Two kernels.
 //
-// Warp roles (672 threads, one CTA per SM):
-//   warps 0-15  row walkers: pooled row r = TMEM lane r is owned by four threads, one per 32-key
-//              quarter of the tile (warp w walks quarter w / 4 of the rows of lane quarter w % 4,
-//              the only lanes it can reach).  Per tile each pulls its 32 estimates into registers
-//              and forms the maxima of its key blocks; the four swap them through shared memory,
-//              so all know the running maximum entering every block; each builds the keep mask
-//              fp32(s + gap) >= m of its quarter; the counts travel with the next tile's maxima
-//              (one meeting per tile), after which each appends its kept keys at its own offset of
-//              the row's list.
-//              (Blocks of 64 or 128 keys span two or four quarters: their maximum is formed from the
-//              quarters' published maxima.)
-//   warps 16-19 producers: cp.async the next K tile (128 contiguous key rows) into a 4-stage ring
-//              of 128-byte-swizzled operand tiles; completion is reported to the stage's mbarrier.
-//   warp  20   MMA issuer (one thread): S_t = Q~ K_t^T, 128 x 128 x 128 as eight tcgen05.mma, into
-//              one of two 128-column accumulator buffers in tensor memory.
-// All hand-offs are mbarriers with bounded waits; a timeout sets VA_STATUS_TIMEOUT.
+// 1. select_mask_kernel: estimate, running maximum and keep test; its result is one keep BIT per
+//    (pooled row, key), written row-major to scratch memory.  The pooled rows of all query heads that
+//    share one KV head form one row list (row R -> head hkv*rep + R/nq, tile R%nq); a CTA owns 128
+//    consecutive rows of that list and walks the keys of its KV head once, 128 keys per tile, in
+//    ascending order, so the running (prefix) maximum of a key-block group is a per-thread register.
+//    Warp roles (576 threads, one CTA per SM):
+//      warps 0-15  row walkers: pooled row r = TMEM lane r is owned by four threads, one per 32-key
+//                 quarter of the tile (warp w walks quarter w / 4 of the rows of lane quarter w % 4,
+//                 the only lanes it can reach).  Per tile each pulls its 32 estimates into registers
+//                 and forms the maxima of its key blocks; the four swap them through shared memory
+//                 (one meeting per tile), so all know the running maximum entering every block;
+//                 each builds the 32-bit keep mask fp32(s + gap) >= m of its quarter.  The words
+//                 are collected in shared memory and leave as 64-byte row pieces every four tiles.
+//      warp 16    one thread streams K: a TMA tensor-map copy per 128-key tile (two boxes of 128 rows
+//                 x 128 bytes, 128-byte swizzle) into a 4-stage ring; rows past the sequence read as zeros.
+//      warp 17    one thread issues S_t = Q~ K_t^T, 128 x 128 x 128 as eight tcgen05.mma, into one of
+//                 four 128-column accumulator buffers in tensor memory.
+//    All hand-offs are mbarriers with bounded waits; a timeout sets VA_STATUS_TIMEOUT.
+//
+// 2. select_expand_kernel: one warp per pooled row turns the row's keep bits into its ascending
+//    index list (population counts, a warp scan, staging in shared memory, coalesced stores) and
+//    writes the row's count.  Lists are deterministic; nothing is zero-filled; no atomics.
 #include "va_common.cuh"
 #include "va_sm100.cuh"
+#include "va_tmap.cuh"
 
 namespace va {
 
@@ -33,8 +35,6 @@ using namespace sm100;
 
 struct SelectParams {
   const void* avg_q;  // (B,H,nq,D)
-  const void* k;
-  int64_t k_sb, k_sh, k_ss;
   const float* gaps;
   int64_t gaps_sb;
   float gap;
@@ -42,6 +42,9 @@ struct SelectParams {
   int32_t* col_idx;
   int64_t capacity;
   int32_t* status;
+  uint32_t* mask;     // keep bits, [(b * kv_heads + hkv) * rows_pad + R][wpad] 32-bit words, bit j of word w = key 32 w + j
+  int rows_pad;       // pooled rows per KV head, rounded up to the CTA height
+  int wpad;           // words per mask row (whole groups of four key tiles)
   int heads, kv_heads, rep, nq, sk;
   int pq, group_k_block;
   int causal, wo_initial, compat_bsq, tile_offset, chunk_tiles;
@@ -52,26 +55,31 @@ namespace {
 constexpr int kRows = 128;   // pooled rows per CTA
 constexpr int kTile = 128;   // keys per tile
 constexpr int kTileBytes = 128 * 256;
-constexpr int kStages = 4;
-constexpr int kThreads = 672;
+constexpr int kStages = 4;   // K ring
+constexpr int kSBufs = 4;    // accumulator buffers in tensor memory (4 x 128 columns = all of it)
+constexpr int kThreads = 576;
 constexpr int kWalkerWarps = 16;
 constexpr size_t kSmem = 1024 + (size_t)kTileBytes * (1 + kStages);
 
 struct Barriers {
-  uint64_t kfull[kStages], kempty[kStages], sfull[2], sempty[2], quad[4];
+  uint64_t kfull[kStages], kempty[kStages], sfull[kSBufs], sempty[kSBufs], quad[4];
 };
 
-// per-row walking state
-struct Row {
-  float run_max, gap;
-  int cnt, hi;
-  int32_t* out;
-};
-
-// 4-byte global store executed only where `pred` is true, without a branch
-__device__ __forceinline__ void st_global_if(int32_t* ptr, int value, bool pred) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p st.global.b32 [%0], %1;\n\t}" ::"l"(ptr), "r"(value), "r"((int)pred)
-               : "memory");
+// End (exclusive) of the keys pooled row `tile` of the chunk may select, spattn/src/kernels/
+// vecattention_kernels.py:231-233,260: all keys, or under the causal rule the keys before the row's
+// diagonal tile; the first row of every compat_bsq rows of a chunk also loses the key blocks that
+// start inside the tile before it, except the first (the reference's truncating division).
+__device__ __forceinline__ int row_key_limit(const SelectParams& p, int tile, int bk) {
+  if (!p.causal) return p.sk;
+  const int64_t g = (int64_t)p.tile_offset + tile;
+  int64_t lim = g * p.pq;
+  const int tile_in_chunk = p.chunk_tiles > 0 ? tile % p.chunk_tiles : tile;
+  if (p.compat_bsq > 0 && (tile_in_chunk % p.compat_bsq) == 0) {
+    const int64_t q1 = (g - 1) * p.pq + bk;
+    lim = q1 < lim ? q1 : lim;
+  }
+  lim = lim < p.sk ? lim : p.sk;
+  return lim > 0 ? (int)lim : 0;
 }
 
 // three-input maximum (one instruction)
@@ -94,51 +102,45 @@ __device__ __forceinline__ float max_of(const uint32_t* v) {
   return fmaxf(a, b);
 }
 
-// Running maximum for the walker of key quarter CQ on a tile that lies wholly inside the walked key
-// range: only the blocks up to its own last one are visited (the thread of the last quarter ends
-// with the value the next tile starts from and publishes it).  pm = own block maxima, xq = the
-// row's published maxima [quarter][block][lane stride 32], gpos = position of the tile's first
-// block inside its group of G blocks.
-template <int BK, int CQ>
-__device__ __forceinline__ void prefix_interior(const float* pm, const float* xq, float& run_max, int gpos, int G, float* rm_own) {
-  constexpr int NP = BK < 32 ? 32 / BK : 1;
-  constexpr int QPB = BK <= 32 ? 1 : BK / 32;                   // key quarters per block (blocks of 64 or 128 keys span several)
-  constexpr int LAST = BK <= 32 ? (CQ + 1) * NP : CQ / QPB + 1;  // blocks up to and including my last
-#pragma unroll
-  for (int k = 0; k < LAST; ++k) {
-    float m;
-    bool mine;
-    if (BK <= 32) {
-      const int q = k / NP, kb = k % NP;
-      mine = q == CQ;
-      m = mine ? pm[kb] : xq[(q * 2 + kb) * 32];
-    } else {  // the block spans QPB quarters
-      mine = k == CQ / QPB;
-      m = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < QPB; ++i) {
-        const int q = k * QPB + i;
-        m = fmaxf(m, q == CQ ? pm[0] : xq[(q * 2) * 32]);
-      }
-    }
-    if (gpos == 0) run_max = -INFINITY;  // a new key-block group starts
-    gpos = gpos + 1 == G ? 0 : gpos + 1;
-    run_max = fmaxf(run_max, m);
-    if (mine) rm_own[BK <= 32 ? k % NP : 0] = run_max;
-  }
+// two fp32 additions in one instruction (round to nearest, no flush: each half is an IEEE add)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t x, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(x));
 }
 
-template <int DT, int BK>
-__global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams p) {
+// BK = k_local_size.  ALIGNED: a key-block group (group_k_block * BK keys) is a whole number of
+// tiles, so groups begin only where tiles begin and a tile inside the walked key range needs no
+// per-block bookkeeping.
+template <int DT, int BK, bool ALIGNED>
+__global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_constant__ CUtensorMap kmap, const SelectParams p) {
   using T = typename Elem<DT>::T;
+  constexpr int SB = BK < 32 ? BK : 32;  // keys per published block maximum
+  constexpr int NP = 32 / SB;            // block maxima a thread forms per tile
+  constexpr int NBT = kTile / BK;        // key blocks per tile
+  constexpr int QPB = BK <= 32 ? 1 : BK / 32;  // key quarters per block (blocks of 64 or 128 keys span several)
   extern __shared__ unsigned char smem_raw[];
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_khi;
   // exchange areas of a row's four threads, double buffered by tile parity (the threads meet once per tile)
   __shared__ float xmax_s[2][4 * 4 * 2 * 32];  // [parity][lane quarter][key quarter][block][lane]: block maxima
-  __shared__ float xrm_s[2][4 * 32];         // [parity][lane quarter][lane]: running maximum after the tile, from the thread of the last key quarter
-  __shared__ int xcnt_s[2][4 * 4 * 32];      // [parity][lane quarter][key quarter][lane]: kept-key counts
+  __shared__ float xq_s[2][4 * 4 * 32];        // [parity][lane quarter][key quarter][lane]: maximum of the quarter
+  // keep words of a group of four tiles, [group parity][word of the row's 16][row]
+  __shared__ uint32_t mstage[2][16][kRows];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int hkv = blockIdx.y, b = blockIdx.z;
@@ -146,31 +148,14 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   // causal rows walk more keys the later their tile: the longest walks are started first
   const int row_base = (p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x) * kRows;
 
-  // ---- per-row state: walker threads (warps 0-15) own row (warp % 4) * 32 + lane ----
+  // ---- per-row limits: walker threads (warps 0-15) own row (warp % 4) * 32 + lane ----
   const bool is_walker = warp < kWalkerWarps;
   const int wrow = (warp & 3) * 32 + lane;
   const int R = row_base + wrow;
   const bool row_ok = is_walker && R < nrows;
   const int h = hkv * p.rep + (row_ok ? R / p.nq : 0);
-  const int tile = row_ok ? R % p.nq : 0;
   const int lo = p.wo_initial ? p.pq : 0;
-  int hi = 0;
-  if (row_ok) {
-    if (!p.causal) {
-      hi = p.sk;
-    } else {
-      const int64_t g = (int64_t)p.tile_offset + tile;
-      int64_t lim = g * p.pq;
-      const int tile_in_chunk = p.chunk_tiles > 0 ? tile % p.chunk_tiles : tile;
-      if (p.compat_bsq > 0 && (tile_in_chunk % p.compat_bsq) == 0) {
-        const int64_t q1 = (g - 1) * p.pq + BK;
-        lim = q1 < lim ? q1 : lim;
-      }
-      lim = lim < p.sk ? lim : p.sk;
-      hi = lim > 0 ? (int)lim : 0;
-    }
-  }
-  const int64_t out_row = ((int64_t)b * p.heads + h) * p.nq + tile;
+  const int hi = row_ok ? row_key_limit(p, R % p.nq, BK) : 0;
 
   if (tid == 0) s_khi = 0;
   __syncthreads();
@@ -184,10 +169,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   const int k_hi = s_khi;                       // CTA-wide end of the key walk
   const int t_lo = lo / kTile;
   const int t_hi = (k_hi + kTile - 1) / kTile;  // exclusive
-  if (t_lo >= t_hi || k_hi <= lo) {             // nothing selectable for any row of this CTA
-    if (row_ok) p.col_count[out_row] = 0;
-    return;
-  }
+  if (t_lo >= t_hi || k_hi <= lo) return;       // nothing selectable for any row of this CTA (the expansion writes zero counts)
 
   unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
   unsigned char* q_s = smem;
@@ -217,18 +199,18 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&bars.kfull[s], 256);  // per producer thread: asynchronous copy-completion arrival + plain arrival
+      mbar_init(&bars.kfull[s], 1);   // the producer's arrival; the copies complete it by byte count
       mbar_init(&bars.kempty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kSBufs; ++s) {
       mbar_init(&bars.sfull[s], 1);
       mbar_init(&bars.sempty[s], kWalkerWarps * 32);
     }
     for (int s = 0; s < 4; ++s) mbar_init(&bars.quad[s], 128);
     fence_proxy_async();
   }
-  if (warp == 20) {
-    tmem_alloc(&tmem_base_s, 256);
+  if (warp == 17) {
+    tmem_alloc(&tmem_base_s, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -237,32 +219,24 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
   const uint32_t tmem = tmem_base_s;
   bool timed_out = false;
 
-  if (warp >= 16 && warp < 20) {
-    // ======================= K tile producers =======================
-    const int pw = warp - 16, hh = lane >> 4, c = lane & 15;
-    const int rbase = 2 * pw + hh;  // this thread copies piece c of rows rbase + 8 i, i = 0..15
-    const uint32_t dst_off = tile_off(128, rbase, c);
-    const T* kbase = static_cast<const T*>(p.k) + b * p.k_sb + hkv * p.k_sh + c * 8;
-    for (int t = t_lo; t < t_hi; ++t) {
-      const int n = t - t_lo, s = n % kStages, u = n / kStages;
-      if (!mbar_wait(&bars.kempty[s], (u & 1) ^ 1)) { timed_out = true; break; }
-      const uint32_t dst = smem_addr(k_s + (size_t)s * kTileBytes) + dst_off;
-      const int key0 = t * kTile + rbase;
-      if (t * kTile + kTile <= p.sk) {
-        const T* src = kbase + (int64_t)key0 * p.k_ss;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) cp_async16_full(dst + i * 1024, src + (int64_t)(8 * i) * p.k_ss);
-      } else {  // last tile: rows past the sequence re-read its last row (finite; the walker ignores them)
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          cp_async16_full(dst + i * 1024, kbase + (int64_t)min(key0 + 8 * i, p.sk - 1) * p.k_ss);
+  if (warp == 16) {
+    // ======================= K tile producer (one thread, TMA) =======================
+    if (lane == 0) {
+      int issued = 0;
+      for (int t = t_lo; t < t_hi; ++t) {
+        const int n = t - t_lo, s = n % kStages, u = n / kStages;
+        if (!mbar_wait(&bars.kempty[s], (u & 1) ^ 1)) { timed_out = true; break; }
+        mbar_expect_tx(&bars.kfull[s], kTileBytes);
+        const uint32_t dst = smem_addr(k_s + (size_t)s * kTileBytes);
+        tma_load_4d(dst, &kmap, 0, t * kTile, hkv, b, &bars.kfull[s]);            // elements 0..63 of the 128 rows
+        tma_load_4d(dst + kTileBytes / 2, &kmap, 64, t * kTile, hkv, b, &bars.kfull[s]);  // elements 64..127
+        issued = n + 1;
       }
-      cp_async_arrive_noinc(&bars.kfull[s]);
-      mbar_arrive(&bars.kfull[s]);
+      if (timed_out) {  // no copy of this CTA may still be in flight when it retires
+        for (int n = max(0, issued - kStages); n < issued; ++n) mbar_wait(&bars.kfull[n % kStages], (n / kStages) & 1);
+      }
     }
-    cp_async_commit();
-    cp_async_wait<0>();  // nothing of this thread may still be in flight when the CTA retires
-  } else if (warp == 20) {
+  } else if (warp == 17) {
     // ======================= MMA issuer =======================
     if (lane == 0) {
       constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
@@ -272,9 +246,8 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) qd[ks] = umma_desc(q_addr + (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32, 16, 1024);
       for (int t = t_lo; t < t_hi; ++t) {
-        const int n = t - t_lo, s = n % kStages, u = n / kStages, sb = n & 1, ub = n >> 1;
+        const int n = t - t_lo, s = n % kStages, u = n / kStages, sb = n % kSBufs, ub = n / kSBufs;
         if (!mbar_wait(&bars.kfull[s], u & 1) || !mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1)) { timed_out = true; break; }
-        fence_proxy_async();
         tc_fence_after();
         const uint32_t k_addr = kr_addr + (uint32_t)s * kTileBytes;
 #pragma unroll
@@ -289,218 +262,260 @@ __global__ void __launch_bounds__(kThreads, 1) select_kernel(const SelectParams 
     // ======================= row walkers =======================
     const int qtr = warp & 3, cq = warp >> 2;  // TMEM lane quarter, key quarter of the tile
     const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
-    Row row;
-    row.run_max = -INFINITY;
-    row.gap = p.gaps ? __ldg(p.gaps + b * p.gaps_sb + h) : p.gap;
-    row.cnt = 0;
-    row.hi = hi;
-    row.out = p.col_idx + out_row * p.capacity;
-    int gpos = (lo / BK) % p.group_k_block;  // position of the next walked block inside its key-block group
+    const float gap = p.gaps ? __ldg(p.gaps + b * p.gaps_sb + h) : p.gap;
+    const uint64_t gap2 = pack2(gap, gap);
     const int G = p.group_k_block;
-    // one key block: group bookkeeping is uniform over the CTA, the rest is per row
-    auto block_begin = [&](int key0) -> bool {
-      if (key0 < lo || key0 >= k_hi) return false;
-      if (gpos == 0) row.run_max = -INFINITY;  // a new key-block group starts
-      gpos = gpos + 1 == G ? 0 : gpos + 1;
-      return true;
+    float run_max = -INFINITY;                // running maximum of the current key-block group, after the previous tile
+    int gpos = ((t_lo * kTile) / BK) % G;     // position of the tile's first block inside its group
+    // this thread's part of the mask rows: the 16-byte piece (lane % 4) of row qtr*32 + cq*8 + lane/4
+    const int frow = qtr * 32 + cq * 8 + (lane >> 2), piece = lane & 3;
+    uint32_t* const fdst = p.mask + ((size_t)(b * p.kv_heads + hkv) * p.rows_pad + row_base + frow) * p.wpad + piece * 4;
+    auto flush_group = [&](int grp) {  // the keep words of tiles 4 grp .. 4 grp + 3 leave as 64 bytes per row
+      const uint32_t(*st)[kRows] = mstage[grp & 1];
+      const uint4 w = make_uint4(st[piece * 4][frow], st[piece * 4 + 1][frow], st[piece * 4 + 2][frow], st[piece * 4 + 3][frow]);
+      *reinterpret_cast<uint4*>(fdst + (size_t)grp * 16) = w;
     };
-    {
-      constexpr int SB = BK < 32 ? BK : 32;  // keys per published maximum
-      constexpr int NP = 32 / SB;            // maxima a thread publishes per tile
-      constexpr int NBT = kTile / BK;        // key blocks per tile
-      // The four threads of a row meet once per tile: the meeting that publishes a tile's block
-      // maxima also carries the previous tile's counts (and the running maximum it ended with), so
-      // a tile's kept keys are appended one tile later, after the positions are known.
-      uint32_t prev_mask = 0u;  // keep mask of the previous tile, not yet appended
-      int prev_key = 0, prev_cnt = 0;
-      auto append_prev = [&](int par) {
-        int before = 0, total = 0;
+    int n_done = 0;
+    for (int t = t_lo; t < t_hi; ++t) {
+      const int n = t - t_lo, sb = n % kSBufs, ub = n / kSBufs, par = n & 1;
+      if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
+      tc_fence_after();
+      const int key_t = t * kTile, key_q = key_t + cq * 32;
+      // ---- my 32 estimates -> registers; the accumulator buffer is free again ----
+      uint32_t v[32];
+      tmem_ld32(tmem + (uint32_t)sb * 128 + lane_base + cq * 32, v);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&bars.sempty[sb]);
+      // ---- maxima of my key blocks (keys past the sequence end never count) ----
+      float pm[NP];
+      if (key_q + 32 <= p.sk) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int cnt_q = q == cq ? prev_cnt : xcnt_s[par][(qtr * 4 + q) * 32 + lane];
-          if (q < cq) before += cnt_q;
-          total += cnt_q;
+        for (int kb = 0; kb < NP; ++kb) pm[kb] = max_of<SB>(v + kb * SB);
+      } else {
+#pragma unroll
+        for (int kb = 0; kb < NP; ++kb) {
+          pm[kb] = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < SB; ++j)
+            if (key_q + kb * SB + j < p.sk) pm[kb] = fmaxf(pm[kb], __uint_as_float(v[kb * SB + j]));
         }
-        int pos = row.cnt + before;
-        row.cnt += total;
-        uint32_t mask = prev_mask;
-        if (row.cnt <= p.capacity) {
-          // The first four kept keys go out as straight-line predicated stores (no divergence: the
-          // lanes of a warp keep different numbers of keys), the rare rest in a loop.
-          int32_t* wp = row.out + pos;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = __ffs((int)mask) - 1;
-            st_global_if(wp + e, prev_key + j, mask != 0u);
-            mask &= mask - 1u;
-          }
-          wp += 4;
-          while (mask) {
-            const int j = __ffs((int)mask) - 1;
-            mask &= mask - 1u;
-            *wp++ = prev_key + j;
-          }
-        } else {
-          while (mask) {
-            const int j = __ffs((int)mask) - 1;
-            mask &= mask - 1u;
-            if (pos < p.capacity) row.out[pos] = prev_key + j;
-            ++pos;
-          }
-        }
-      };
-      int n_done = 0;
-      for (int t = t_lo; t < t_hi; ++t) {
-        const int n = t - t_lo, sb = n & 1, ub = n >> 1, par = n & 1;
-        if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
-        tc_fence_after();
-        const int key_t = t * kTile, key_q = key_t + cq * 32;
-        // ---- my 32 estimates -> registers; the accumulator buffer is free again ----
-        uint32_t v[32];
-        tmem_ld32(tmem + (uint32_t)sb * 128 + lane_base + cq * 32, v);
-        tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(&bars.sempty[sb]);
-        // ---- maxima of my key blocks (keys past the sequence end never count) ----
-        float pm[NP];
-        if (key_q + 32 <= p.sk) {
-#pragma unroll
-          for (int kb = 0; kb < NP; ++kb) pm[kb] = max_of<SB>(v + kb * SB);
-        } else {
-#pragma unroll
-          for (int kb = 0; kb < NP; ++kb) {
-            pm[kb] = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < SB; ++j)
-              if (key_q + kb * SB + j < p.sk) pm[kb] = fmaxf(pm[kb], __uint_as_float(v[kb * SB + j]));
-          }
-        }
+      }
+      // a tile inside the walked key range (all but the first and last of a CTA) needs no range tests
+      const bool fast = ALIGNED && key_t >= lo && key_t + kTile <= k_hi;
+      float qmax = pm[0];
+      if (NP == 2) qmax = fmaxf(pm[0], pm[NP - 1]);
+      if (fast) {
+        xq_s[par][(qtr * 4 + cq) * 32 + lane] = qmax;
+      } else {
 #pragma unroll
         for (int kb = 0; kb < NP; ++kb) xmax_s[par][((qtr * 4 + cq) * 2 + kb) * 32 + lane] = pm[kb];
-        mbar_arrive(&bars.quad[qtr]);
-        if (!mbar_wait(&bars.quad[qtr], par)) { timed_out = true; break; }
-        if (n > 0) {  // the previous tile: where it ended and where its keys go
-          row.run_max = xrm_s[par ^ 1][qtr * 32 + lane];
-          append_prev(par ^ 1);
-        }
-        // ---- running maximum entering / after every block of the tile, identical in the four threads ----
-        // A tile inside the walked key range (all but the first and last of a CTA) needs no range
-        // tests and lets each thread stop at its own last block.
-        const bool interior = key_t >= lo && key_t + kTile <= k_hi;
-        float rm_own[NP];
-        bool on_own[NP];
-        if (interior) {
-          const float* xq = xmax_s[par] + (qtr * 4 * 2) * 32 + lane;
-          switch (cq) {
-            case 0: prefix_interior<BK, 0>(pm, xq, row.run_max, gpos, G, rm_own); break;
-            case 1: prefix_interior<BK, 1>(pm, xq, row.run_max, gpos, G, rm_own); break;
-            case 2: prefix_interior<BK, 2>(pm, xq, row.run_max, gpos, G, rm_own); break;
-            default: prefix_interior<BK, 3>(pm, xq, row.run_max, gpos, G, rm_own); break;
-          }
+      }
+      mbar_arrive(&bars.quad[qtr]);
+      if (!mbar_wait(&bars.quad[qtr], par)) { timed_out = true; break; }
+      if (n > 0 && (t & 3) == 0) flush_group((t >> 2) - 1);  // all four threads of every row have passed the previous group
+      // ---- running maximum entering / after each of my blocks, identical in a row's four threads ----
+      float rm_own[NP];
+      bool on_own[NP];
+      if (fast) {
+        if (gpos == 0) run_max = -INFINITY;  // a new key-block group starts with this tile
+        float q[4];
 #pragma unroll
-          for (int kb = 0; kb < NP; ++kb) on_own[kb] = true;
-          gpos += NBT;
-          while (gpos >= G) gpos -= G;
+        for (int j = 0; j < 4; ++j) q[j] = xq_s[par][(qtr * 4 + j) * 32 + lane];
+        if (BK <= 32) {
+          float before = run_max;
+#pragma unroll
+          for (int j = 0; j < 3; ++j)
+            if (j < cq) before = fmaxf(before, q[j]);
+          rm_own[0] = fmaxf(before, pm[0]);
+          if (NP == 2) rm_own[NP - 1] = fmaxf(rm_own[0], pm[NP - 1]);
+        } else if (BK == 64) {  // my block is the quarter pair (cq / 2)
+          const float first = fmaxf(q[0], q[1]);
+          rm_own[0] = cq < 2 ? fmaxf(run_max, first) : fmax3(run_max, first, fmaxf(q[2], q[3]));
         } else {
+          rm_own[0] = fmax3(run_max, fmaxf(q[0], q[1]), fmaxf(q[2], q[3]));
+        }
+        run_max = fmax3(run_max, fmaxf(q[0], q[1]), fmaxf(q[2], q[3]));
 #pragma unroll
-          for (int k = 0; k < NBT; ++k) {
-            float m;
-            bool mine;
-            if constexpr (BK <= 32) {
-              const int q = k / NP, kb = k % NP;  // the quarter that holds block k and its place there
-              mine = q == cq;
-              m = mine ? pm[kb] : xmax_s[par][((qtr * 4 + q) * 2 + kb) * 32 + lane];
-            } else {  // the block spans QPB quarters
-              constexpr int QPB = BK / 32;
-              mine = k == cq / QPB;
-              m = -INFINITY;
+        for (int kb = 0; kb < NP; ++kb) on_own[kb] = true;
+      } else {
+        int gp = gpos;
 #pragma unroll
-              for (int i = 0; i < QPB; ++i) {
-                const int q = k * QPB + i;
-                m = fmaxf(m, q == cq ? pm[0] : xmax_s[par][((qtr * 4 + q) * 2) * 32 + lane]);
-              }
-            }
-            const bool on = block_begin(key_t + k * BK);
-            if (on) row.run_max = fmaxf(row.run_max, m);
-            if (mine) {
-              rm_own[BK <= 32 ? k % NP : 0] = row.run_max;
-              on_own[BK <= 32 ? k % NP : 0] = on;
+        for (int k = 0; k < NBT; ++k) {
+          float m;
+          bool mine;
+          if constexpr (BK <= 32) {
+            const int qq = k / NP, kb = k % NP;  // the quarter that holds block k and its place there
+            mine = qq == cq;
+            m = mine ? pm[kb] : xmax_s[par][((qtr * 4 + qq) * 2 + kb) * 32 + lane];
+          } else {  // the block spans QPB quarters
+            mine = k == cq / QPB;
+            m = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < QPB; ++i) {
+              const int qq = k * QPB + i;
+              m = fmaxf(m, qq == cq ? pm[0] : xmax_s[par][((qtr * 4 + qq) * 2) * 32 + lane]);
             }
           }
+          const int key0 = key_t + k * BK;
+          const bool on = key0 >= lo && key0 < k_hi;
+          if (on) {
+            if (gp == 0) run_max = -INFINITY;  // a new key-block group starts
+            run_max = fmaxf(run_max, m);
+          }
+          gp = gp + 1 == G ? 0 : gp + 1;
+          if (mine) {
+            rm_own[BK <= 32 ? k % NP : 0] = run_max;
+            on_own[BK <= 32 ? k % NP : 0] = on;
+          }
         }
-        if (cq == 3) xrm_s[par][qtr * 32 + lane] = row.run_max;  // the value the next tile starts from
-        // ---- keep mask of my 32 keys.  fp32(s + gap) >= m  <=>  the difference fp32(s + gap) - m is
-        // not negative (a difference of two floats has the exact sign); its sign bit is shifted
-        // into the mask, last key first, so key c ends up in bit c.  Two additions on the FMA pipe
-        // and one funnel shift per estimate: the integer pipe is the busy one in this kernel. ----
-        uint32_t neg = 0u;
+      }
+      gpos += NBT;
+      while (gpos >= G) gpos -= G;
+      // ---- keep mask of my 32 keys: fp32(s + gap) >= m  <=>  fp32(s + gap) - m is not negative (the
+      // difference of two floats has the exact sign).  Two packed additions per pair of estimates and
+      // one funnel shift per estimate that moves the sign bit into the mask, last key first, so key c
+      // ends up in bit c. ----
+      uint32_t neg = 0u;
 #pragma unroll
-        for (int c = 31; c >= 0; --c) {
-          const float d = __fsub_rn(__fadd_rn(__uint_as_float(v[c]), row.gap), rm_own[c / SB]);
-          neg = __funnelshift_l(__float_as_uint(d), neg, 1);
+      for (int kb = NP - 1; kb >= 0; --kb) {
+        const uint64_t nm2 = pack2(-rm_own[kb], -rm_own[kb]);
+#pragma unroll
+        for (int c = kb * SB + SB - 1; c > kb * SB; c -= 2) {
+          uint32_t d_lo, d_hi;
+          unpack2(add2(add2(pack2u(v[c - 1], v[c]), gap2), nm2), d_lo, d_hi);
+          neg = __funnelshift_l(d_hi, neg, 1);
+          neg = __funnelshift_l(d_lo, neg, 1);
         }
-        uint32_t mask = ~neg;
+      }
+      uint32_t mask = ~neg;
+      if (!fast) {
 #pragma unroll
         for (int kb = 0; kb < NP; ++kb)
           if (!on_own[kb]) mask &= ~((SB == 32 ? 0xffffffffu : ((1u << SB) - 1u)) << (kb * SB));
-        const int room = row.hi - key_q;  // keys at or past the row's limit are cut off
-        if (room < 32) mask = room <= 0 ? 0u : (mask & ((1u << room) - 1u));
-        prev_mask = mask;
-        prev_key = key_q;
-        prev_cnt = __popc(mask);
-        xcnt_s[par][(qtr * 4 + cq) * 32 + lane] = prev_cnt;
-        n_done = n + 1;
       }
-      // ---- the last tile's keys: one more meeting for its counts ----
-      if (!timed_out && n_done > 0) {
-        mbar_arrive(&bars.quad[qtr]);
-        if (mbar_wait(&bars.quad[qtr], n_done & 1)) append_prev((n_done - 1) & 1);
-        else timed_out = true;
-      }
+      const int room = hi - key_q;  // keys at or past the row's limit are cut off
+      if (room < 32) mask = room <= 0 ? 0u : (mask & ((1u << room) - 1u));
+      mstage[(t >> 2) & 1][(t & 3) * 4 + cq][wrow] = mask;
+      n_done = n + 1;
     }
-    if (row_ok && !timed_out && cq == 0) {  // the row's count is written by the thread of the first quarter
-      p.col_count[out_row] = row.cnt;
-      if (row.cnt > p.capacity && p.status) atomicOr(p.status, VA_STATUS_OVERFLOW);
+    // ---- the last group of tiles: one more meeting, then its words leave ----
+    if (!timed_out && n_done > 0) {
+      mbar_arrive(&bars.quad[qtr]);
+      if (mbar_wait(&bars.quad[qtr], n_done & 1)) flush_group((t_hi - 1) >> 2);
+      else timed_out = true;
     }
   }
   if (timed_out && p.status) atomicOr(p.status, VA_STATUS_TIMEOUT);
   tc_fence_before();
   __syncthreads();
-  if (warp == 20) tmem_dealloc(tmem, 256);
+  if (warp == 17) tmem_dealloc(tmem, 512);
+}
+
+// ---- keep bits -> ascending index lists ---------------------------------------------------------
+// One warp per pooled row (b, h, tile).  Per step the lanes take 32 consecutive mask words (1024
+// keys), a warp scan of their population counts gives every lane the place of its keys, the keys
+// are staged in shared memory and leave as contiguous stores.  The mask kernel has already cleared
+// every bit outside the row's key range.
+constexpr int kExpandWarps = 8;
+
+template <int BK>
+__global__ void __launch_bounds__(kExpandWarps * 32) select_expand_kernel(const SelectParams p, int64_t total_rows) {
+  __shared__ int32_t stage_s[kExpandWarps][1024];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = (int64_t)blockIdx.x * kExpandWarps + warp;  // = (b * heads + h) * nq + tile
+  if (row >= total_rows) return;
+  const int tile = (int)(row % p.nq);
+  const int64_t bh = row / p.nq;
+  const int h = (int)(bh % p.heads), b = (int)(bh / p.heads);
+  const int hkv = h / p.rep;
+  const int R = (h % p.rep) * p.nq + tile;
+  const int lo = p.wo_initial ? p.pq : 0;
+  const int hi = row_key_limit(p, tile, BK);
+  const uint32_t* mrow = p.mask + ((size_t)(b * p.kv_heads + hkv) * p.rows_pad + R) * p.wpad;
+  int32_t* out = p.col_idx + row * p.capacity;
+  int32_t* stage = stage_s[warp];
+  int64_t cnt = 0;
+  if (hi > lo) {
+    const int w_lo = lo >> 5, w_hi = (hi + 31) >> 5;
+    uint32_t cur = w_lo + lane < w_hi ? __ldg(mrow + w_lo + lane) : 0u;
+    for (int w0 = w_lo; w0 < w_hi; w0 += 32) {
+      const uint32_t nxt = w0 + 32 + lane < w_hi ? __ldg(mrow + w0 + 32 + lane) : 0u;  // the next step's words, fetched early
+      uint32_t word = cur;
+      const int c = __popc(word);
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const int total = __shfl_sync(0xffffffffu, incl, 31);
+      if (total > 0) {
+        int sp = incl - c;
+        const int key0 = (w0 + lane) << 5;
+        while (word) {
+          stage[sp++] = key0 + __ffs((int)word) - 1;
+          word &= word - 1u;
+        }
+        __syncwarp();
+        for (int i = lane; i < total; i += 32)
+          if (cnt + i < p.capacity) out[cnt + i] = stage[i];
+        __syncwarp();
+        cnt += total;
+      }
+      cur = nxt;
+    }
+  }
+  if (lane == 0) {
+    p.col_count[row] = (int32_t)cnt;
+    if (cnt > p.capacity && p.status) atomicOr(p.status, VA_STATUS_OVERFLOW);
+  }
 }
 
 template <int DT, int BK>
-int launch_bk(const SelectParams& p, int batch, cudaStream_t stream) {
+int launch_bk(const SelectParams& p, const CUtensorMap& kmap, int batch, cudaStream_t stream) {
+  const bool aligned = ((int64_t)p.group_k_block * BK) % kTile == 0;
+  auto kern = aligned ? select_mask_kernel<DT, BK, true> : select_mask_kernel<DT, BK, false>;
   // per-device attribute; setting it on every launch keeps multi-device processes correct
-  if (cudaFuncSetAttribute(select_kernel<DT, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess)
-    return VA_ERR_CUDA;
-  const int nrows = p.rep * p.nq;
-  dim3 grid((nrows + kRows - 1) / kRows, p.kv_heads, batch);
-  select_kernel<DT, BK><<<grid, kThreads, kSmem, stream>>>(p);
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess) return VA_ERR_CUDA;
+  dim3 grid(p.rows_pad / kRows, p.kv_heads, batch);
+  kern<<<grid, kThreads, kSmem, stream>>>(kmap, p);
+  if (cudaGetLastError() != cudaSuccess) return VA_ERR_CUDA;
+  const int64_t total_rows = (int64_t)batch * p.heads * p.nq;
+  select_expand_kernel<BK><<<(unsigned)((total_rows + kExpandWarps - 1) / kExpandWarps), kExpandWarps * 32, 0, stream>>>(p, total_rows);
   return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
 }
 
 template <int DT>
-int launch_dt(const SelectParams& p, int bk, int batch, cudaStream_t stream) {
+int launch_dt(const SelectParams& p, const CUtensorMap& kmap, int bk, int batch, cudaStream_t stream) {
   switch (bk) {
-    case 16: return launch_bk<DT, 16>(p, batch, stream);
-    case 32: return launch_bk<DT, 32>(p, batch, stream);
-    case 64: return launch_bk<DT, 64>(p, batch, stream);
-    case 128: return launch_bk<DT, 128>(p, batch, stream);
+    case 16: return launch_bk<DT, 16>(p, kmap, batch, stream);
+    case 32: return launch_bk<DT, 32>(p, kmap, batch, stream);
+    case 64: return launch_bk<DT, 64>(p, kmap, batch, stream);
+    case 128: return launch_bk<DT, 128>(p, kmap, batch, stream);
     default: return VA_ERR_SHAPE;
   }
 }
 
 }  // namespace
 
+// mask rows per KV head and words per mask row for a selection of nq pooled rows per head over sk keys
+static inline void mask_geometry(int heads, int kv_heads, int nq, int sk, int& rows_pad, int& wpad) {
+  const int nrows = (heads / kv_heads) * nq;
+  rows_pad = (nrows + kRows - 1) / kRows * kRows;
+  const int tiles = (sk + kTile - 1) / kTile;
+  wpad = (tiles + 3) / 4 * 16;
+}
+
+size_t select_workspace_bytes(int batch, int heads, int kv_heads, int nq, int sk) {
+  int rows_pad, wpad;
+  mask_geometry(heads, kv_heads, nq, sk, rows_pad, wpad);
+  return (size_t)batch * kv_heads * rows_pad * wpad * 4;
+}
 
 int select(const va_select_args& a, cudaStream_t stream) {
   SelectParams p;
   p.avg_q = a.avg_q;
-  p.k = a.k.ptr;
-  p.k_sb = a.k.stride_b;
-  p.k_sh = a.k.stride_h;
-  p.k_ss = a.k.stride_s;
   p.gaps = a.gaps;
   p.gaps_sb = a.gaps_stride_b;
   p.gap = a.gap;
@@ -520,7 +535,16 @@ int select(const va_select_args& a, cudaStream_t stream) {
   p.compat_bsq = a.compat_bsq;
   p.tile_offset = a.tile_offset;
   p.chunk_tiles = a.chunk_tiles;
-  return a.dtype == VA_BF16 ? launch_dt<VA_BF16>(p, a.bk, a.batch, stream) : launch_dt<VA_FP16>(p, a.bk, a.batch, stream);
+  mask_geometry(a.heads, a.kv_heads, a.nq, a.sk, p.rows_pad, p.wpad);
+  if (!a.workspace) return VA_ERR_NULL;
+  if (a.workspace_bytes < select_workspace_bytes(a.batch, a.heads, a.kv_heads, a.nq, a.sk)) return VA_ERR_CAPACITY;
+  if ((reinterpret_cast<uintptr_t>(a.workspace) & 15u) != 0) return VA_ERR_ALIGN;
+  p.mask = static_cast<uint32_t*>(a.workspace);
+  CUtensorMap kmap;
+  if (!encode_rows_map(&kmap, a.dtype == VA_BF16, a.k.ptr, a.batch, a.kv_heads, a.sk, a.k.stride_b, a.k.stride_h, a.k.stride_s,
+                       kTile))
+    return VA_ERR_CUDA;
+  return a.dtype == VA_BF16 ? launch_dt<VA_BF16>(p, kmap, a.bk, a.batch, stream) : launch_dt<VA_FP16>(p, kmap, a.bk, a.batch, stream);
 }
 
 }  // namespace va
