@@ -29,6 +29,8 @@
 #include "va_sm100.cuh"
 #include "va_tmap.cuh"
 
+#include <type_traits>
+
 namespace va {
 
 using namespace sm100;
@@ -62,7 +64,8 @@ constexpr int kWalkerWarps = 16;
 constexpr size_t kSmem = 1024 + (size_t)kTileBytes * (1 + kStages);
 
 struct Barriers {
-  uint64_t kfull[kStages], kempty[kStages], sfull[kSBufs], sempty[kSBufs], quad[4];
+  uint64_t kfull[kStages], kempty[kStages], sfull[kSBufs], sempty[kSBufs];
+  uint64_t hand[4][4];  // [lane quarter][turn]: that warp has published the rows' running maximum after its tile
 };
 
 // End (exclusive) of the keys pooled row `tile` of the chunk may select, spattn/src/kernels/
@@ -122,25 +125,176 @@ __device__ __forceinline__ void unpack2(uint64_t x, uint32_t& lo, uint32_t& hi) 
   asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(x));
 }
 
+// ---- the row walkers ------------------------------------------------------------------------------
+// Sixteen warps; warp (qtr, turn) = (w % 4, w / 4) owns the pooled rows of TMEM lane quarter qtr (a warp
+// reaches only the quarter w % 4) on every fourth key tile, n = turn (mod 4), which lives in accumulator
+// buffer `turn`.  A thread handles its row's whole tile: first the maxima of the tile's key blocks
+// (independent of earlier tiles), then, once the warp of the previous tile has handed over the rows'
+// running maximum, the running maximum entering every block, which it hands on at once, and last the
+// keep bits of the 128 keys, read from tensor memory a second time.  The four warps of a quarter sit on one
+// scheduler and are in different phases of different tiles, so one's latencies hide behind another's work.
+struct WalkShared {
+  float rmx[4][4][32];  // [lane quarter][turn][lane]: running maximum after that warp's latest tile
+};
+
+// what a walker thread knows about its CTA and its row
+struct WalkArgs {
+  uint32_t tmem;       // first accumulator buffer
+  int t_lo, t_hi;      // key tiles the CTA walks
+  int lo, k_hi;        // key range the CTA walks
+  int sk, hi;          // sequence length; end of this thread's row
+  int G;               // key blocks per group
+  float gap;
+  uint32_t* mrow;      // this thread's mask row
+};
+
+// one wait, cheap when the phase is already complete
+__device__ __forceinline__ bool wait_fast(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait(bar, parity);
+}
+
+// Keep bits of 32 estimates: fp32(s + gap) >= m  <=>  fp32(s + gap) - m is not negative (the difference of
+// two floats has the exact sign).  m_lo applies to estimates 0..15, m_hi to 16..31.  Two packed additions per
+// pair of estimates and one funnel shift per estimate that moves the sign bit into the mask, last key first,
+// so key c ends up in bit c.
+__device__ __forceinline__ uint32_t keep_bits(const uint32_t (&v)[32], uint64_t gap2, float m_lo, float m_hi) {
+  uint32_t neg = 0u;
+#pragma unroll
+  for (int half = 1; half >= 0; --half) {
+    const float m = half ? m_hi : m_lo;
+    const uint64_t nm2 = pack2(-m, -m);
+#pragma unroll
+    for (int c = half * 16 + 15; c > half * 16; c -= 2) {
+      uint32_t d_lo, d_hi;
+      unpack2(add2(add2(pack2u(v[c - 1], v[c]), gap2), nm2), d_lo, d_hi);
+      neg = __funnelshift_l(d_hi, neg, 1);
+      neg = __funnelshift_l(d_lo, neg, 1);
+    }
+  }
+  return ~neg;
+}
+
+// Walk every fourth key tile of the CTA for the rows of lane quarter `qtr`.  Returns false if a wait ran
+// out.  BK = k_local_size; ALIGNED: groups of key blocks begin only where tiles begin.
+template <int BK, bool ALIGNED>
+__device__ __forceinline__ bool walk_rows(const WalkArgs& a, Barriers& bars, WalkShared& sh, int qtr, int turn, int lane) {
+  constexpr int NBT = kTile / BK;  // key blocks per tile
+  const uint32_t taddr = a.tmem + ((uint32_t)(qtr * 32) << 16) + (uint32_t)turn * 128;
+  const uint64_t gap2 = pack2(a.gap, a.gap);
+  uint64_t* const sfull = &bars.sfull[turn];
+  uint64_t* const sempty = &bars.sempty[turn];
+  uint64_t* const hand_in = &bars.hand[qtr][(turn + 3) & 3];
+  uint64_t* const hand_out = &bars.hand[qtr][turn];
+  const float* rm_in = &sh.rmx[qtr][(turn + 3) & 3][lane];
+  float* rm_out = &sh.rmx[qtr][turn][lane];
+  const int ntiles = a.t_hi - a.t_lo;
+  const unsigned tpg = ALIGNED ? (unsigned)(((int64_t)a.G * BK) / kTile) : 1u;  // tiles per group of key blocks
+  const int t_in_lo = (a.lo + kTile - 1) / kTile;  // first tile wholly at or after lo
+  const int t_in_hi = min(a.k_hi, a.sk) / kTile;   // tiles before this one end at or before k_hi
+
+  for (int n = turn; n < ntiles; n += 4) {
+    const int t = a.t_lo + n, key_t = t * kTile;
+    const uint32_t par = (uint32_t)(n >> 2) & 1u;
+    const bool inner = ALIGNED && t >= t_in_lo && t < t_in_hi;  // no range tests, no group start inside the tile
+    if (!wait_fast(sfull, par)) return false;
+    tc_fence_after();
+    // ---- maxima of the tile's key blocks (keys past the sequence end never count) ----
+    float pm[NBT];
+#pragma unroll
+    for (int k = 0; k < NBT; ++k) pm[k] = -INFINITY;
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c4 * 32, v);
+      tmem_wait_ld();
+      if (key_t + c4 * 32 + 32 <= a.sk) {
+        if (BK == 16) {
+          pm[(2 * c4) % NBT] = max_of<16>(v);
+          pm[(2 * c4 + 1) % NBT] = max_of<16>(v + 16);
+        } else {
+          const int k = (c4 * 32 / BK) % NBT;
+          pm[k] = fmaxf(pm[k], max_of<32>(v));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (key_t + c4 * 32 + j < a.sk) {
+            const int k = ((c4 * 32 + j) / BK) % NBT;
+            pm[k] = fmaxf(pm[k], __uint_as_float(v[j]));
+          }
+      }
+    }
+    // ---- the rows' running maximum after the previous tile, from the warp that walked it ----
+    float run = -INFINITY;
+    if (n > 0) {
+      if (!wait_fast(hand_in, (uint32_t)((n - 1) >> 2) & 1u)) return false;
+      run = *rm_in;
+    }
+    // ---- running maximum entering / after every block; handed on before the keep bits are formed ----
+    float rm[NBT];
+    uint32_t on_bits = 0xffffffffu;  // bit k: block k lies inside the walked key range
+    if (inner) {
+      if ((unsigned)t % tpg == 0u) run = -INFINITY;  // a new group of key blocks starts with this tile
+#pragma unroll
+      for (int k = 0; k < NBT; ++k) {
+        run = fmaxf(run, pm[k]);
+        rm[k] = run;
+      }
+    } else {
+      int gp = (int)((unsigned)(key_t / BK) % (unsigned)a.G);  // position of the tile's first block inside its group
+      on_bits = 0u;
+#pragma unroll
+      for (int k = 0; k < NBT; ++k) {
+        const int key0 = key_t + k * BK;
+        if (key0 >= a.lo && key0 < a.k_hi) {
+          if (gp == 0) run = -INFINITY;  // a new group of key blocks starts
+          run = fmaxf(run, pm[k]);
+          on_bits |= 1u << k;
+        }
+        gp = gp + 1 == a.G ? 0 : gp + 1;
+        rm[k] = run;
+      }
+    }
+    *rm_out = run;
+    mbar_arrive(hand_out);
+    // ---- keep bits of the 128 keys ----
+    uint32_t w[4];
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c4 * 32, v);
+      tmem_wait_ld();
+      if (c4 == 3) {  // the accumulator buffer is free again
+        tc_fence_before();
+        mbar_arrive(sempty);
+      }
+      const int k_lo = BK == 16 ? 2 * c4 : (c4 * 32 / BK) % NBT, k_hi16 = BK == 16 ? 2 * c4 + 1 : k_lo;
+      uint32_t m = keep_bits(v, gap2, rm[k_lo % NBT], rm[k_hi16 % NBT]);
+      if (!inner) {
+        if (!((on_bits >> (k_lo % NBT)) & 1u)) m &= 0xffff0000u;
+        if (!((on_bits >> (k_hi16 % NBT)) & 1u)) m &= 0x0000ffffu;
+      }
+      const int room = a.hi - (key_t + c4 * 32);  // keys at or past the row's limit are cut off
+      if (room < 32) m = room <= 0 ? 0u : (m & ((1u << room) - 1u));
+      w[c4] = m;
+    }
+    *reinterpret_cast<uint4*>(a.mrow + (size_t)t * 4) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  return true;
+}
+
 // BK = k_local_size.  ALIGNED: a key-block group (group_k_block * BK keys) is a whole number of
 // tiles, so groups begin only where tiles begin and a tile inside the walked key range needs no
 // per-block bookkeeping.
 template <int DT, int BK, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_constant__ CUtensorMap kmap, const SelectParams p) {
   using T = typename Elem<DT>::T;
-  constexpr int SB = BK < 32 ? BK : 32;  // keys per published block maximum
-  constexpr int NP = 32 / SB;            // block maxima a thread forms per tile
-  constexpr int NBT = kTile / BK;        // key blocks per tile
-  constexpr int QPB = BK <= 32 ? 1 : BK / 32;  // key quarters per block (blocks of 64 or 128 keys span several)
   extern __shared__ unsigned char smem_raw[];
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_khi;
-  // exchange areas of a row's four threads, double buffered by tile parity (the threads meet once per tile)
-  __shared__ float xmax_s[2][4 * 4 * 2 * 32];  // [parity][lane quarter][key quarter][block][lane]: block maxima
-  __shared__ float xq_s[2][4 * 4 * 32];        // [parity][lane quarter][key quarter][lane]: maximum of the quarter
-  // keep words of a group of four tiles, [group parity][word of the row's 16][row]
-  __shared__ uint32_t mstage[2][16][kRows];
+  __shared__ WalkShared wsh;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int hkv = blockIdx.y, b = blockIdx.z;
@@ -204,9 +358,9 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
     }
     for (int s = 0; s < kSBufs; ++s) {
       mbar_init(&bars.sfull[s], 1);
-      mbar_init(&bars.sempty[s], kWalkerWarps * 32);
+      mbar_init(&bars.sempty[s], 4 * 32);  // the four warps (one per lane quarter) that walk the buffer's tiles
     }
-    for (int s = 0; s < 4; ++s) mbar_init(&bars.quad[s], 128);
+    for (int s = 0; s < 16; ++s) mbar_init(&bars.hand[s >> 2][s & 3], 32);
     fence_proxy_async();
   }
   if (warp == 17) {
@@ -260,151 +414,18 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
     }
   } else {
     // ======================= row walkers =======================
-    const int qtr = warp & 3, cq = warp >> 2;  // TMEM lane quarter, key quarter of the tile
-    const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
-    const float gap = p.gaps ? __ldg(p.gaps + b * p.gaps_sb + h) : p.gap;
-    const uint64_t gap2 = pack2(gap, gap);
-    const int G = p.group_k_block;
-    float run_max = -INFINITY;                // running maximum of the current key-block group, after the previous tile
-    int gpos = ((t_lo * kTile) / BK) % G;     // position of the tile's first block inside its group
-    // this thread's part of the mask rows: the 16-byte piece (lane % 4) of row qtr*32 + cq*8 + lane/4
-    const int frow = qtr * 32 + cq * 8 + (lane >> 2), piece = lane & 3;
-    uint32_t* const fdst = p.mask + ((size_t)(b * p.kv_heads + hkv) * p.rows_pad + row_base + frow) * p.wpad + piece * 4;
-    auto flush_group = [&](int grp) {  // the keep words of tiles 4 grp .. 4 grp + 3 leave as 64 bytes per row
-      const uint32_t(*st)[kRows] = mstage[grp & 1];
-      const uint4 w = make_uint4(st[piece * 4][frow], st[piece * 4 + 1][frow], st[piece * 4 + 2][frow], st[piece * 4 + 3][frow]);
-      *reinterpret_cast<uint4*>(fdst + (size_t)grp * 16) = w;
-    };
-    int n_done = 0;
-    for (int t = t_lo; t < t_hi; ++t) {
-      const int n = t - t_lo, sb = n % kSBufs, ub = n / kSBufs, par = n & 1;
-      if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
-      tc_fence_after();
-      const int key_t = t * kTile, key_q = key_t + cq * 32;
-      // ---- my 32 estimates -> registers; the accumulator buffer is free again ----
-      uint32_t v[32];
-      tmem_ld32(tmem + (uint32_t)sb * 128 + lane_base + cq * 32, v);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&bars.sempty[sb]);
-      // ---- maxima of my key blocks (keys past the sequence end never count) ----
-      float pm[NP];
-      if (key_q + 32 <= p.sk) {
-#pragma unroll
-        for (int kb = 0; kb < NP; ++kb) pm[kb] = max_of<SB>(v + kb * SB);
-      } else {
-#pragma unroll
-        for (int kb = 0; kb < NP; ++kb) {
-          pm[kb] = -INFINITY;
-#pragma unroll
-          for (int j = 0; j < SB; ++j)
-            if (key_q + kb * SB + j < p.sk) pm[kb] = fmaxf(pm[kb], __uint_as_float(v[kb * SB + j]));
-        }
-      }
-      // a tile inside the walked key range (all but the first and last of a CTA) needs no range tests
-      const bool fast = ALIGNED && key_t >= lo && key_t + kTile <= k_hi;
-      float qmax = pm[0];
-      if (NP == 2) qmax = fmaxf(pm[0], pm[NP - 1]);
-      if (fast) {
-        xq_s[par][(qtr * 4 + cq) * 32 + lane] = qmax;
-      } else {
-#pragma unroll
-        for (int kb = 0; kb < NP; ++kb) xmax_s[par][((qtr * 4 + cq) * 2 + kb) * 32 + lane] = pm[kb];
-      }
-      mbar_arrive(&bars.quad[qtr]);
-      if (!mbar_wait(&bars.quad[qtr], par)) { timed_out = true; break; }
-      if (n > 0 && (t & 3) == 0) flush_group((t >> 2) - 1);  // all four threads of every row have passed the previous group
-      // ---- running maximum entering / after each of my blocks, identical in a row's four threads ----
-      float rm_own[NP];
-      bool on_own[NP];
-      if (fast) {
-        if (gpos == 0) run_max = -INFINITY;  // a new key-block group starts with this tile
-        float q[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) q[j] = xq_s[par][(qtr * 4 + j) * 32 + lane];
-        if (BK <= 32) {
-          float before = run_max;
-#pragma unroll
-          for (int j = 0; j < 3; ++j)
-            if (j < cq) before = fmaxf(before, q[j]);
-          rm_own[0] = fmaxf(before, pm[0]);
-          if (NP == 2) rm_own[NP - 1] = fmaxf(rm_own[0], pm[NP - 1]);
-        } else if (BK == 64) {  // my block is the quarter pair (cq / 2)
-          const float first = fmaxf(q[0], q[1]);
-          rm_own[0] = cq < 2 ? fmaxf(run_max, first) : fmax3(run_max, first, fmaxf(q[2], q[3]));
-        } else {
-          rm_own[0] = fmax3(run_max, fmaxf(q[0], q[1]), fmaxf(q[2], q[3]));
-        }
-        run_max = fmax3(run_max, fmaxf(q[0], q[1]), fmaxf(q[2], q[3]));
-#pragma unroll
-        for (int kb = 0; kb < NP; ++kb) on_own[kb] = true;
-      } else {
-        int gp = gpos;
-#pragma unroll
-        for (int k = 0; k < NBT; ++k) {
-          float m;
-          bool mine;
-          if constexpr (BK <= 32) {
-            const int qq = k / NP, kb = k % NP;  // the quarter that holds block k and its place there
-            mine = qq == cq;
-            m = mine ? pm[kb] : xmax_s[par][((qtr * 4 + qq) * 2 + kb) * 32 + lane];
-          } else {  // the block spans QPB quarters
-            mine = k == cq / QPB;
-            m = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < QPB; ++i) {
-              const int qq = k * QPB + i;
-              m = fmaxf(m, qq == cq ? pm[0] : xmax_s[par][((qtr * 4 + qq) * 2) * 32 + lane]);
-            }
-          }
-          const int key0 = key_t + k * BK;
-          const bool on = key0 >= lo && key0 < k_hi;
-          if (on) {
-            if (gp == 0) run_max = -INFINITY;  // a new key-block group starts
-            run_max = fmaxf(run_max, m);
-          }
-          gp = gp + 1 == G ? 0 : gp + 1;
-          if (mine) {
-            rm_own[BK <= 32 ? k % NP : 0] = run_max;
-            on_own[BK <= 32 ? k % NP : 0] = on;
-          }
-        }
-      }
-      gpos += NBT;
-      while (gpos >= G) gpos -= G;
-      // ---- keep mask of my 32 keys: fp32(s + gap) >= m  <=>  fp32(s + gap) - m is not negative (the
-      // difference of two floats has the exact sign).  Two packed additions per pair of estimates and
-      // one funnel shift per estimate that moves the sign bit into the mask, last key first, so key c
-      // ends up in bit c. ----
-      uint32_t neg = 0u;
-#pragma unroll
-      for (int kb = NP - 1; kb >= 0; --kb) {
-        const uint64_t nm2 = pack2(-rm_own[kb], -rm_own[kb]);
-#pragma unroll
-        for (int c = kb * SB + SB - 1; c > kb * SB; c -= 2) {
-          uint32_t d_lo, d_hi;
-          unpack2(add2(add2(pack2u(v[c - 1], v[c]), gap2), nm2), d_lo, d_hi);
-          neg = __funnelshift_l(d_hi, neg, 1);
-          neg = __funnelshift_l(d_lo, neg, 1);
-        }
-      }
-      uint32_t mask = ~neg;
-      if (!fast) {
-#pragma unroll
-        for (int kb = 0; kb < NP; ++kb)
-          if (!on_own[kb]) mask &= ~((SB == 32 ? 0xffffffffu : ((1u << SB) - 1u)) << (kb * SB));
-      }
-      const int room = hi - key_q;  // keys at or past the row's limit are cut off
-      if (room < 32) mask = room <= 0 ? 0u : (mask & ((1u << room) - 1u));
-      mstage[(t >> 2) & 1][(t & 3) * 4 + cq][wrow] = mask;
-      n_done = n + 1;
-    }
-    // ---- the last group of tiles: one more meeting, then its words leave ----
-    if (!timed_out && n_done > 0) {
-      mbar_arrive(&bars.quad[qtr]);
-      if (mbar_wait(&bars.quad[qtr], n_done & 1)) flush_group((t_hi - 1) >> 2);
-      else timed_out = true;
-    }
+    WalkArgs a;
+    a.tmem = tmem;
+    a.t_lo = t_lo;
+    a.t_hi = t_hi;
+    a.lo = lo;
+    a.k_hi = k_hi;
+    a.sk = p.sk;
+    a.hi = hi;
+    a.G = p.group_k_block;
+    a.gap = p.gaps ? __ldg(p.gaps + b * p.gaps_sb + h) : p.gap;
+    a.mrow = p.mask + ((size_t)(b * p.kv_heads + hkv) * p.rows_pad + row_base + wrow) * p.wpad;
+    timed_out = !walk_rows<BK, ALIGNED>(a, bars, wsh, warp & 3, warp >> 2, lane);
   }
   if (timed_out && p.status) atomicOr(p.status, VA_STATUS_TIMEOUT);
   tc_fence_before();
