@@ -156,23 +156,26 @@ __device__ __forceinline__ bool wait_fast(uint64_t* bar, uint32_t parity) {
 
 // Keep bits of 32 estimates: fp32(s + gap) >= m  <=>  fp32(s + gap) - m is not negative (the difference of
 // two floats has the exact sign).  m_lo applies to estimates 0..15, m_hi to 16..31.  Two packed additions per
-// pair of estimates and one funnel shift per estimate that moves the sign bit into the mask, last key first,
-// so key c ends up in bit c.
+// pair of estimates and one funnel shift per estimate that moves the sign bit into a byte of the mask, last key
+// first; four independent chains of eight shifts, joined by byte permutes, so key c ends up in bit c.
 __device__ __forceinline__ uint32_t keep_bits(const uint32_t (&v)[32], uint64_t gap2, float m_lo, float m_hi) {
-  uint32_t neg = 0u;
+  uint32_t neg[4];
 #pragma unroll
-  for (int half = 1; half >= 0; --half) {
-    const float m = half ? m_hi : m_lo;
+  for (int q = 3; q >= 0; --q) {
+    const float m = q >= 2 ? m_hi : m_lo;
     const uint64_t nm2 = pack2(-m, -m);
+    uint32_t x = 0u;
 #pragma unroll
-    for (int c = half * 16 + 15; c > half * 16; c -= 2) {
+    for (int c = q * 8 + 7; c > q * 8; c -= 2) {
       uint32_t d_lo, d_hi;
       unpack2(add2(add2(pack2u(v[c - 1], v[c]), gap2), nm2), d_lo, d_hi);
-      neg = __funnelshift_l(d_hi, neg, 1);
-      neg = __funnelshift_l(d_lo, neg, 1);
+      x = __funnelshift_l(d_hi, x, 1);
+      x = __funnelshift_l(d_lo, x, 1);
     }
+    neg[q] = x;  // eight sign bits in the low byte
   }
-  return ~neg;
+  const uint32_t lo16 = __byte_perm(neg[0], neg[1], 0x0040), hi16 = __byte_perm(neg[2], neg[3], 0x0040);
+  return ~__byte_perm(lo16, hi16, 0x5410);
 }
 
 // Walk every fourth key tile of the CTA for the rows of lane quarter `qtr`.  Returns false if a wait ran
@@ -376,15 +379,17 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
   if (warp == 16) {
     // ======================= K tile producer (one thread, TMA) =======================
     if (lane == 0) {
-      int issued = 0;
+      int issued = 0, s = 0;
+      uint32_t epar = 1;  // phase parity of the stage's "empty" barrier
+      const uint32_t k_base = smem_addr(k_s);
       for (int t = t_lo; t < t_hi; ++t) {
-        const int n = t - t_lo, s = n % kStages, u = n / kStages;
-        if (!mbar_wait(&bars.kempty[s], (u & 1) ^ 1)) { timed_out = true; break; }
+        if (!wait_fast(&bars.kempty[s], epar)) { timed_out = true; break; }
         mbar_expect_tx(&bars.kfull[s], kTileBytes);
-        const uint32_t dst = smem_addr(k_s + (size_t)s * kTileBytes);
-        tma_load_4d(dst, &kmap, 0, t * kTile, hkv, b, &bars.kfull[s]);            // elements 0..63 of the 128 rows
+        const uint32_t dst = k_base + (uint32_t)s * kTileBytes;
+        tma_load_4d(dst, &kmap, 0, t * kTile, hkv, b, &bars.kfull[s]);                    // elements 0..63 of the 128 rows
         tma_load_4d(dst + kTileBytes / 2, &kmap, 64, t * kTile, hkv, b, &bars.kfull[s]);  // elements 64..127
-        issued = n + 1;
+        issued = t - t_lo + 1;
+        if (++s == kStages) { s = 0; epar ^= 1u; }
       }
       if (timed_out) {  // no copy of this CTA may still be in flight when it retires
         for (int n = max(0, issued - kStages); n < issued; ++n) mbar_wait(&bars.kfull[n % kStages], (n / kStages) & 1);
@@ -395,21 +400,17 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
     if (lane == 0) {
       constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
       constexpr uint32_t idesc = umma_idesc(128, 128, in16, 0, 0);
-      const uint32_t q_addr = smem_addr(q_s), kr_addr = smem_addr(k_s);
-      uint64_t qd[8];
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) qd[ks] = umma_desc(q_addr + (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32, 16, 1024);
+      const uint64_t qd = umma_desc(smem_addr(q_s), 16, 1024), kd0 = umma_desc(smem_addr(k_s), 16, 1024);
+      int s = 0, sb = 0;
+      uint32_t kpar = 0, spar = 1;  // phase parities of the stage's "full" and the buffer's "empty" barrier
       for (int t = t_lo; t < t_hi; ++t) {
-        const int n = t - t_lo, s = n % kStages, u = n / kStages, sb = n % kSBufs, ub = n / kSBufs;
-        if (!mbar_wait(&bars.kfull[s], u & 1) || !mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1)) { timed_out = true; break; }
+        if (!wait_fast(&bars.kfull[s], kpar) || !wait_fast(&bars.sempty[sb], spar)) { timed_out = true; break; }
         tc_fence_after();
-        const uint32_t k_addr = kr_addr + (uint32_t)s * kTileBytes;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma(tmem + (uint32_t)sb * 128, qd[ks],
-               umma_desc(k_addr + (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32, 16, 1024), idesc, ks > 0);
+        umma_k128_rows128(tmem + (uint32_t)sb * 128, qd, kd0 + (uint64_t)(s * (kTileBytes >> 4)), idesc);
         umma_commit(&bars.kempty[s]);
         umma_commit(&bars.sfull[sb]);
+        if (++s == kStages) { s = 0; kpar ^= 1u; }
+        if (++sb == kSBufs) { sb = 0; spar ^= 1u; }
       }
     }
   } else {

@@ -147,6 +147,27 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// D[tmem] = A[smem] * B[smem] over K = 128 as eight K16 steps, for operand tiles of 128 rows in the half-tile
+// pair layout (both K-major): step ks reads 32 bytes further along the rows, steps 4..7 read the second half.
+// a0 / b0 are the descriptors of step 0; only their address field (16-byte units) moves.  One instruction
+// sequence without per-step descriptor arithmetic in C++: the issuing thread shares its scheduler with busy
+// warps, so every instruction it does not execute shortens the time between tiles.
+__device__ __forceinline__ void umma_k128_rows128(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 a, b;\n\t"
+      "setp.ne.b32 p, %3, %3;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "setp.eq.b32 p, %3, %3;\n\t"
+      "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p;\n\t"
+      "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p;\n\t"
+      "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p;\n\t"
+      "add.u64 a, %1, 1024;\n\tadd.u64 b, %2, 1024;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p;\n\t"
+      "add.u64 a, %1, 1026;\n\tadd.u64 b, %2, 1026;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p;\n\t"
+      "add.u64 a, %1, 1028;\n\tadd.u64 b, %2, 1028;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p;\n\t"
+      "add.u64 a, %1, 1030;\n\tadd.u64 b, %2, 1030;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a0), "l"(b0), "r"(idesc)
+      : "memory");
+}
 // the mbarrier receives one arrival when every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
