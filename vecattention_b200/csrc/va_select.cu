@@ -8,7 +8,7 @@
 //    share one KV head form one row list (row R -> head hkv*rep + R/nq, tile R%nq); a CTA owns 128
 //    consecutive rows of that list and walks the keys of its KV head once, 128 keys per tile, in
 //    ascending order, so the running (prefix) maximum of a key-block group is a per-thread register.
-//    Warp roles (576 threads, one CTA per SM):
+//    Warp roles (608 threads, one CTA per SM):
 //      warps 0-15  row walkers: pooled row r = TMEM lane r is owned by four threads, one per 32-key
 //                 quarter of the tile (warp w walks quarter w / 4 of the rows of lane quarter w % 4,
 //                 the only lanes it can reach).  Per tile each pulls its 32 estimates into registers
@@ -18,8 +18,8 @@
 //                 are collected in shared memory and leave as 64-byte row pieces every four tiles.
 //      warp 16    one thread streams K: a TMA tensor-map copy per 128-key tile (two boxes of 128 rows
 //                 x 128 bytes, 128-byte swizzle) into a 4-stage ring; rows past the sequence read as zeros.
-//      warp 17    one thread issues S_t = Q~ K_t^T, 128 x 128 x 128 as eight tcgen05.mma, into one of
-//                 four 128-column accumulator buffers in tensor memory.
+//      warps 17,18 one thread each issues S_t = Q~ K_t^T for alternate tiles, 128 x 128 x 128 as eight
+//                 tcgen05.mma, into one of four 128-column accumulator buffers in tensor memory.
 //    All hand-offs are mbarriers with bounded waits; a timeout sets VA_STATUS_TIMEOUT.
 //
 // 2. select_expand_kernel: one warp per pooled row turns the row's keep bits into its ascending
@@ -59,7 +59,7 @@ constexpr int kTile = 128;   // keys per tile
 constexpr int kTileBytes = 128 * 256;
 constexpr int kStages = 4;   // K ring
 constexpr int kSBufs = 4;    // accumulator buffers in tensor memory (4 x 128 columns = all of it)
-constexpr int kThreads = 576;
+constexpr int kThreads = 608;  // 16 walker warps, the K producer, two MMA issuers
 constexpr int kWalkerWarps = 16;
 constexpr size_t kSmem = 1024 + (size_t)kTileBytes * (1 + kStages);
 
@@ -395,22 +395,24 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
         for (int n = max(0, issued - kStages); n < issued; ++n) mbar_wait(&bars.kfull[n % kStages], (n / kStages) & 1);
       }
     }
-  } else if (warp == 17) {
-    // ======================= MMA issuer =======================
+  } else if (warp >= 17) {
+    // ======================= MMA issuers =======================
+    // Two threads (warps 17 and 18) take alternate tiles: while one is held by the tensor pipe's queue, the
+    // other has already passed the barrier waits of the next tile, so the pipe never runs dry between tiles.
     if (lane == 0) {
       constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
       constexpr uint32_t idesc = umma_idesc(128, 128, in16, 0, 0);
       const uint64_t qd = umma_desc(smem_addr(q_s), 16, 1024), kd0 = umma_desc(smem_addr(k_s), 16, 1024);
-      int s = 0, sb = 0;
+      int s = warp - 17, sb = warp - 17;
       uint32_t kpar = 0, spar = 1;  // phase parities of the stage's "full" and the buffer's "empty" barrier
-      for (int t = t_lo; t < t_hi; ++t) {
+      for (int t = t_lo + (warp - 17); t < t_hi; t += 2) {
         if (!wait_fast(&bars.kfull[s], kpar) || !wait_fast(&bars.sempty[sb], spar)) { timed_out = true; break; }
         tc_fence_after();
         umma_k128_rows128(tmem + (uint32_t)sb * 128, qd, kd0 + (uint64_t)(s * (kTileBytes >> 4)), idesc);
         umma_commit(&bars.kempty[s]);
         umma_commit(&bars.sfull[sb]);
-        if (++s == kStages) { s = 0; kpar ^= 1u; }
-        if (++sb == kSBufs) { sb = 0; spar ^= 1u; }
+        if ((s += 2) >= kStages) { s -= kStages; kpar ^= 1u; }
+        if ((sb += 2) >= kSBufs) { sb -= kSBufs; spar ^= 1u; }
       }
     }
   } else {
