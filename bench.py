@@ -1,17 +1,18 @@
 #!/usr/bin/env python
 """Benchmark of the VecAttention prefill hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|mini]
-                    [--scaling weak|strong] [--impl graft|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c3|c2|c5|mini]
+                    [--scaling strong|weak] [--impl graft|reference]
 
 A step is one call of ``VecAttention_prefill`` (pool -> select -> vector-sparse attention) over
-one layer's q/k/v of the named synthetic workload.  ``value`` is effective TFLOP/s: the FLOPs of
-the selected (query tile, key) pairs only, 4 * rows * head_dim per pair, summed over all ranks,
+one layer's q/k/v of the named synthetic workload (default: the 118.8 K-token video-DiT shape, the
+largest configuration that fits one GPU).  ``value`` is effective TFLOP/s: the FLOPs of the
+selected (query tile, key) pairs only, 4 * rows * head_dim per pair, summed over all ranks,
 divided by the slowest rank's device time.  One JSON line is printed by rank 0.
 
-Under ``torchrun`` (N > 1) every rank drives one GPU.  ``--scaling weak`` (default): every rank
-runs the whole single-GPU workload on its own draw of the data (no communication at all);
-``--scaling strong``: the heads of one layer are sharded across the ranks.
+Under ``torchrun`` (N > 1) every rank drives one GPU.  ``--scaling strong`` (default): the heads of
+the one layer are sharded across the ranks, whole KV groups per rank, no communication on the
+path; ``--scaling weak``: every rank runs the whole single-GPU workload on its own draw of the data.
 
 ``--impl reference`` times the CPU restatement of the reference's PyTorch path (the oracle) with
 all host threads on a bounded sample of the same workload; rank 0 only.
@@ -147,8 +148,9 @@ def cpu_sample(name: str, threshold: float, tiles: int, sample_seed: int = 0):
     return wl, wl.q[:, :, :rows].contiguous()
 
 
-def run_cpu_sample(wl, q_rows, threshold: float):
-    """One pass of the oracle over the sample; returns (seconds, effective FLOPs)."""
+def run_cpu_sample(wl, q_rows, threshold: float, keep: bool = False):
+    """One pass of the oracle over the sample; returns (seconds, effective FLOPs) and, with ``keep``, also the
+    output and the per-tile selection counts."""
     from oracle import vecattn_oracle as O
     t0 = time.perf_counter()
     if wl.causal:
@@ -168,6 +170,8 @@ def run_cpu_sample(wl, q_rows, threshold: float):
             rows = min(pq, q_rows.shape[2] - t * pq)
             flops += 4.0 * D * rows * c
             t += 1
+    if keep:
+        return dt, flops, out, torch.cat([cc for cc, _ in sel], dim=2)
     return dt, flops
 
 
@@ -221,12 +225,187 @@ def _calibrate_cpu(wl, q_rows, O) -> float:
     return math.sqrt(lo * hi)
 
 
+def _calibrated_threshold(va, wl, args):
+    """MinP threshold that reaches the workload's keep ratio on this data (untimed)."""
+    from vecattention_b200.synth import calibrate_threshold
+    if args.threshold:
+        return args.threshold
+    pq, bk, g = wl.q_pooling_size, wl.k_local_size, wl.group_k_block
+    avg_all = va.average_vector(wl.q, pq)
+    rep = wl.heads // wl.kv_heads
+
+    def counts_at(th, hslice):
+        kv = slice(hslice.start // rep, max(1, hslice.stop // rep))
+        cnt, _ = va.fuse_qk_softmax_minp_wo_causal(avg_all[:, hslice].contiguous(), wl.k[:, kv], 0,
+                                                   -math.log(th + 1e-9), wl.causal, pq, bk, wo_initial=wl.causal,
+                                                   group_k_block=g, trim=False, capacity=4)
+        return cnt
+    return calibrate_threshold(wl, counts_at)
+
+
+def _stage_times(va, api, wl, thr, counts, bcnt, bidx, out):
+    """Per-kernel times through the same entry points the operator uses, the way the operator runs them: one
+    launch per stage for the whole sequence when its index lists fit the single-pass budget, else chunk by chunk."""
+    pq, bk, g, chunk = wl.q_pooling_size, wl.k_local_size, wl.group_k_block, wl.chunk_size
+    avg = va.average_vector(wl.q, pq)
+    t_pool = time_cuda(lambda: va.average_vector(wl.q, pq), 3, 10)
+    idx_all = wl.batch * wl.heads * wl.nq * ((wl.seq_len + 3) // 4 * 4) * 4
+    free, _ = torch.cuda.mem_get_info()
+    step_rows = wl.seq_len if idx_all <= min(32 << 30, int(free * 0.4)) else chunk
+    sel_ms = att_ms = 0.0
+    gap = -math.log(thr + 1e-9)
+    for i in range(0, wl.seq_len, step_rows):
+        t0, t1 = i // pq, min(wl.nq, -(-(i + step_rows) // pq))
+        avg_c = avg[:, :, t0:t1].contiguous()
+        sel = lambda: va.fuse_qk_softmax_minp_wo_causal(avg_c, wl.k, t0, gap, wl.causal, pq, bk, wo_initial=wl.causal,
+                                                        group_k_block=g, trim=False)
+        cc, ci = sel()
+        sel_ms += time_cuda(sel, 2, 5)
+        sk_eff = min(wl.seq_len, i + step_rows) if wl.causal else wl.seq_len
+        qc, oc = wl.q[:, :, i:i + step_rows], out[:, :, i:i + step_rows]
+        bc, bi = bcnt[:, :, t0:t1].contiguous(), bidx[:, :, t0:t1].contiguous()
+        att = lambda: api._sparse_attn_bhsd(qc, wl.k[:, :, :sk_eff], wl.v[:, :, :sk_eff], pq, bc, bi, cc, ci,
+                                            wl.causal, q_offset=i, out=oc)
+        att_ms += time_cuda(att, 2, 5)
+        del cc, ci
+    return {"pool_ms": t_pool, "select_ms": sel_ms, "attn_ms": att_ms}
+
+
+def _rooflines(wl, peaks, stage, flops, counts):
+    esz = 2
+    kept_total = float(counts.sum())
+    sel_bytes = (wl.q.numel() + wl.k.numel()) * esz + 4 * kept_total + 4 * counts.numel()
+    achieved_tf = flops / (stage["attn_ms"] * 1e-3) / 1e12
+    traffic = NCU_TRAFFIC_PER_HEAD_32K * wl.heads if wl.name in ("c2", "c2h8") else None
+    roofline = {"kernel": "sparse_attn64_kernel" if wl.q_pooling_size == 64 else "sparse_attn_kernel", "bound": "tensor",
+                "achieved": achieved_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": achieved_tf / peaks["bf16_tflops"], "traffic": traffic,
+                "traffic_note": ("ncu capture of 8 heads x 32 K tokens, scaled by heads" if traffic else
+                                 "captured on the 8-head 32 K case only (profiles/); DRAM traffic there equals the "
+                                 "algorithmic bytes"),
+                "peak_source": peaks["_source"] + " burst"}
+    sel_gbs = sel_bytes / ((stage["pool_ms"] + stage["select_ms"]) * 1e-3) / 1e9
+    est_flops = 2.0 * wl.nq * wl.seq_len * D * wl.heads * wl.batch * (0.5 if wl.causal else 1.0)
+    roofline_select = {"kernel": "pool_q_kernel+select_mask_kernel+select_expand_kernel", "bound": "hbm", "achieved": sel_gbs,
+                       "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"],
+                       "algorithmic_bytes": sel_bytes, "peak_source": peaks["_source"],
+                       "estimate_tflops": est_flops / (stage["select_ms"] * 1e-3) / 1e12,
+                       "estimate_frac_of_tensor_peak": est_flops / (stage["select_ms"] * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+    return roofline, roofline_select
+
+
+def _dense_baseline(wl):
+    """Dense attention on the same GPU, for context: the best of the library kernels that run here, on four
+    heads, scaled to all heads.  Returns (ms, which)."""
+    hd = min(wl.heads, 4)
+    rep = wl.heads // wl.kv_heads
+    qd = wl.q[:, :hd]
+    kd = wl.k[:, : max(1, hd // rep)].repeat_interleave(min(rep, hd), dim=1)[:, :hd]
+    vd = wl.v[:, : max(1, hd // rep)].repeat_interleave(min(rep, hd), dim=1)[:, :hd]
+    best, which, tried = None, None, {}
+    cands = {"torch_sdpa": lambda: torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, is_causal=wl.causal)}
+    try:
+        from flash_attn import flash_attn_func
+        qf, kf, vf = (x.transpose(1, 2).contiguous() for x in (qd, kd, vd))
+        cands["flash_attn"] = lambda: flash_attn_func(qf, kf, vf, causal=wl.causal)
+    except Exception:  # noqa: BLE001
+        pass
+    try:
+        import flashinfer
+        q1, k1, v1 = (x[0].transpose(0, 1).contiguous() for x in (qd, kd, vd))
+        cands["flashinfer"] = lambda: flashinfer.single_prefill_with_kv_cache(q1, k1, v1, causal=wl.causal)
+    except Exception:  # noqa: BLE001
+        pass
+    for name, f in cands.items():
+        try:
+            ms = time_cuda(f, 1, 3) * wl.heads / hd
+            tried[name] = ms
+            if best is None or ms < best:
+                best, which = ms, name
+        except Exception as e:  # noqa: BLE001 - a library kernel that does not run on this GPU is skipped
+            tried[name] = f"unavailable: {type(e).__name__}"
+            torch.cuda.synchronize()
+    return best, which, tried
+
+
+def _reference_triton_select_ms(wl, thr):
+    """The reference's own Triton selection (installed under baseline/_ref) on the same inputs, chunk by chunk
+    as its operator calls it: the in-family GPU kernel the selection stage is measured against.  None if the
+    reference is not installed or does not run."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "spattn")) or wl.heads != wl.kv_heads:
+        return None, "reference not installed under baseline/_ref" if wl.heads == wl.kv_heads else "reference has no GQA"
+    try:
+        import types
+        if ref_dir not in sys.path:
+            sys.path.insert(0, ref_dir)
+        stub = types.ModuleType("vllm_flash_attn")
+        stub.sparse_attn_func = None
+        sys.modules.setdefault("vllm_flash_attn", stub)
+        from spattn.src.kernels.vecattention_kernels import fuse_qk_softmax_minp_wo_causal as ref_select
+        from spattn.src.utils import average_vector as ref_pool
+        pq, bk, g, chunk = wl.q_pooling_size, wl.k_local_size, wl.group_k_block, wl.chunk_size
+        gap = -math.log(thr + 1e-9)
+
+        def run():
+            for i in range(0, wl.seq_len, chunk):
+                avg = ref_pool(wl.q[:, :, i:i + chunk], pq, use_triton=True)
+                ref_select(avg, wl.k, i // pq, gap, wl.causal, pq, bk, wo_initial=wl.causal, group_k_block=g)
+        return time_cuda(run, 1, 2), "average_vector(use_triton=True) + fuse_qk_softmax_minp_wo_causal per chunk"
+    except Exception as e:  # noqa: BLE001
+        torch.cuda.synchronize()
+        return None, f"reference Triton selection did not run: {type(e).__name__}: {e}"[:200]
+
+
+def _measure(va, api, wl, thr, args, barrier, status, out):
+    """Warm-up, then exactly ``args.steps`` timed steps bracketed by barrier + synchronize.  Returns ms for all steps."""
+    pq, bk, g, chunk = wl.q_pooling_size, wl.k_local_size, wl.group_k_block, wl.chunk_size
+
+    def step():
+        va.VecAttention_prefill(wl.q, wl.k, wl.v, thr, pq, bk, g, wl.causal, chunk, out=out, status=status)
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    if args.profile_window:
+        torch.cuda.profiler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    if args.profile_window:
+        torch.cuda.profiler.stop()
+    return e0.elapsed_time(e1)
+
+
+def _launches_per_step(wl):
+    idx_all_bytes = wl.batch * wl.heads * wl.nq * ((wl.seq_len + 3) // 4 * 4) * 4
+    free, _ = torch.cuda.mem_get_info()
+    n_chunks = 1 if idx_all_bytes <= min(32 << 30, int(free * 0.4)) else math.ceil(wl.seq_len / wl.chunk_size)
+    return n_chunks * 5  # pool + selection (two kernels) + block tables + attention per pass
+
+
+def _parity_on_cpu_sample(va, cwl, q_rows, thr, ref_out, ref_counts, dev):
+    """The CUDA operator on the tensors of the CPU sample against the oracle's result for them."""
+    causal = cwl.causal
+    k = cwl.k[:, :1, : q_rows.shape[2]] if causal else cwl.k[:, :1]
+    v = cwl.v[:, :1, : q_rows.shape[2]] if causal else cwl.v[:, :1]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out, counts = va.VecAttention_prefill(q_rows.to(dev), k.to(dev), v.to(dev), thr, cwl.q_pooling_size, cwl.k_local_size,
+                                          cwl.group_k_block, causal, cwl.chunk_size, return_selection=True, status=status)
+    err = (out.float().cpu() - ref_out.float()).abs()
+    return {"count_diffs": int((counts.cpu() - ref_counts).abs().sum()), "selected_pairs": int(ref_counts.sum()),
+            "max_abs": float(err.max()), "mean_abs": float(err.mean()), "status_word": int(status.item()),
+            "checker": "CPU oracle on the cpu_baseline sample (selection pinned to the reference; attention parity unpinned)"}
+
+
 def graft_arm(args):
     import torch.distributed as dist
     import vecattention_b200 as va
     from vecattention_b200 import api
     from vecattention_b200.sharding import local_slices
-    from vecattention_b200.synth import calibrate_threshold, make_workload
+    from vecattention_b200.synth import CONFIGS, make_workload
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -243,76 +422,39 @@ def graft_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    from vecattention_b200.synth import CONFIGS
     cfg = CONFIGS[args.workload]
-    if args.scaling == "strong" and world > 1:
+    strong = args.scaling == "strong"
+    if strong and world > cfg["kv_heads"]:
+        raise SystemExit(f"{args.workload} has {cfg['kv_heads']} KV groups: it cannot be sharded over {world} GPUs")
+    if strong and world > 1:
         hs, _ = local_slices(cfg["heads"], cfg["kv_heads"], rank, world)
         wl = make_workload(args.workload, device=dev, heads=range(hs.start, hs.stop))
     else:
         wl = make_workload(args.workload, device=dev, sample_seed=rank)
     pq, bk, g, chunk = wl.q_pooling_size, wl.k_local_size, wl.group_k_block, wl.chunk_size
-
-    # ---- threshold calibrated to the configuration's keep ratio (untimed) ----
-    if args.threshold:
-        thr = args.threshold
-    else:
-        avg_all = va.average_vector(wl.q, pq)
-        rep = wl.heads // wl.kv_heads
-
-        def counts_at(th, hslice):
-            kv = slice(hslice.start // rep, max(1, hslice.stop // rep))
-            cnt, _ = va.fuse_qk_softmax_minp_wo_causal(avg_all[:, hslice].contiguous(), wl.k[:, kv], 0,
-                                                       -math.log(th + 1e-9), wl.causal, pq, bk, wo_initial=wl.causal,
-                                                       group_k_block=g, trim=False, capacity=4)
-            return cnt
-        thr = calibrate_threshold(wl, counts_at)
-        del avg_all
+    thr = _calibrated_threshold(va, wl, args)
+    if world > 1 and strong and not args.threshold:  # one threshold for the layer: rank 0's calibration
+        t = torch.tensor([thr], dtype=torch.float64, device=dev)
+        dist.broadcast(t, 0)
+        thr = float(t[0])
     out = torch.empty_like(wl.q)
-
-    def step():
-        va.VecAttention_prefill(wl.q, wl.k, wl.v, thr, pq, bk, g, wl.causal, chunk, out=out)
-
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
     _, counts = va.VecAttention_prefill(wl.q, wl.k, wl.v, thr, pq, bk, g, wl.causal, chunk, return_selection=True)
     bcnt, bidx = api.block_tables(wl.batch, wl.heads, wl.seq_len, pq, wl.causal, dev)
     flops = effective_flops(counts, wl, bcnt if wl.causal else None)
-    kept = float(counts.sum()) / (wl.eligible_pairs_per_head() * wl.heads * wl.batch)
+    kept_pairs = float(counts.sum())
+    launches = args.steps * _launches_per_step(wl)
 
     # ---- timed region: exactly K steps, device time, max over ranks ----
     with ClockSampler(local_rank) as clk:
-        for _ in range(args.warmup):
-            step()
-        barrier()
-        if args.profile_window:
-            torch.cuda.profiler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        barrier()
-        if args.profile_window:
-            torch.cuda.profiler.stop()
-    ms_total = e0.elapsed_time(e1)
+        ms_total = _measure(va, api, wl, thr, args, barrier, status, out)
     clocks = clk.summary()
-    t = torch.tensor([ms_total, flops], dtype=torch.float64, device=dev)
-    if world > 1:
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = t.clone()
-        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        ms_total, flops_all = float(tmax[0]), float(tsum[1])
-    else:
-        flops_all = flops
-    ms_step = ms_total / args.steps
-    value = flops_all / (ms_step * 1e-3) / 1e12
-    idx_all_bytes = wl.batch * wl.heads * wl.nq * ((wl.seq_len + 3) // 4 * 4) * 4
-    n_chunks = 1 if idx_all_bytes <= (32 << 30) else math.ceil(wl.seq_len / chunk)
-    launches = args.steps * n_chunks * 4  # pool + select + block tables + attention per chunk
 
-    # ---- end to end through the public API with host buffers, on every rank at once: q, k, v start
-    # in pinned host memory and the output ends there, every step; the host entry point pipelines head
-    # slices (copy in / compute / copy out) over three streams.  Device time, max over ranks. ----
-    e2e = None
+    # ---- end to end through the public API with host buffers, on every rank at once: q, k, v start in pinned
+    # host memory and the output ends there, every step; the host entry point pipelines head slices (copy in /
+    # compute / copy out) over three streams.  Device time, max over ranks. ----
+    e2e_ms = e2e_err = 0.0
+    h2d = d2h = 0
     if not args.profile_window:
         esz_ = wl.q.element_size()
         qh, kh, vh = (x.cpu().pin_memory() for x in (wl.q, wl.k, wl.v))
@@ -331,124 +473,113 @@ def graft_arm(args):
             e2e_step()
         f1.record()
         barrier()
+        e2e_ms = f0.elapsed_time(f1) / n_e2e
         e2e_err = float((oh.to(out.device).float() - out.float()).abs().max())
         h2d = (qh.numel() + kh.numel() + vh.numel()) * esz_
         d2h = oh.numel() * esz_
-        te = torch.tensor([f0.elapsed_time(f1) / n_e2e, e2e_err, float(h2d), float(d2h)], dtype=torch.float64, device=dev)
-        if world > 1:
-            temax = te.clone()
-            dist.all_reduce(temax, op=dist.ReduceOp.MAX)
-            tesum = te.clone()
-            dist.all_reduce(tesum, op=dist.ReduceOp.SUM)
-            e2e_ms, e2e_err, h2d, d2h = float(temax[0]), float(temax[1]), int(tesum[2]), int(tesum[3])
-        else:
-            e2e_ms = float(te[0])
-        e2e = {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "max_abs_diff_vs_device_call": e2e_err,
-               "note": "VecAttention_prefill_host on every rank at once: pinned host q/k/v in, pinned host output "
-                       "out, head slices pipelined over three streams; device time, max over ranks"}
         del staging, qh, kh, vh, oh
 
-    line = None
-    if rank == 0 and args.profile_window:
-        line = {"metric": "vecattention_prefill_effective_tflops", "value": value, "unit": "TFLOP/s",
-                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-                "config": {"workload": wl.name, "threshold": thr, "keep_ratio": kept},
-                "note": "profile window run: per-kernel, end-to-end and CPU legs skipped"}
-    elif rank == 0:
-        peaks = load_peaks()
-        # ---- per-kernel times (same entry points the operator uses), rank 0 ----
-        avg = va.average_vector(wl.q, pq)
-        t_pool = time_cuda(lambda: va.average_vector(wl.q, pq), 3, 10)
-        stage = {"pool_ms": t_pool}
-        nqc = math.ceil(min(chunk, wl.seq_len) / pq)
-        sel_ms, att_ms = 0.0, 0.0
-        # stages are timed the way the operator runs them: one launch for the whole sequence when its
-        # index lists fit the single-pass budget, else chunk by chunk
-        idx_all = wl.batch * wl.heads * wl.nq * ((wl.seq_len + 3) // 4 * 4) * 4
-        step_rows = wl.seq_len if idx_all <= (32 << 30) else chunk
-        for i in range(0, wl.seq_len, step_rows):
-            t0, t1 = i // pq, min(wl.nq, -(-(i + step_rows) // pq))
-            avg_c = avg[:, :, t0:t1].contiguous()
-            gap = -math.log(thr + 1e-9)
-            sel = lambda: va.fuse_qk_softmax_minp_wo_causal(avg_c, wl.k, t0, gap, wl.causal, pq, bk,
-                                                            wo_initial=wl.causal, group_k_block=g, trim=False)
-            cc, ci = sel()
-            sel_ms += time_cuda(sel, 2, 5)
-            sk_eff = min(wl.seq_len, i + step_rows) if wl.causal else wl.seq_len
-            qc = wl.q[:, :, i:i + step_rows]
-            oc = out[:, :, i:i + step_rows]
-            bc, bi = bcnt[:, :, t0:t1].contiguous(), bidx[:, :, t0:t1].contiguous()
-            att = lambda: api._sparse_attn_bhsd(qc, wl.k[:, :, :sk_eff], wl.v[:, :, :sk_eff], pq, bc, bi, cc, ci,
-                                                wl.causal, q_offset=i, out=oc)
-            att_ms += time_cuda(att, 2, 5)
-            del cc, ci
-        stage.update(select_ms=sel_ms, attn_ms=att_ms)
-        esz = 2
-        kept_total = float(counts.sum())
-        sel_bytes = (wl.q.numel() + wl.k.numel()) * esz + 4 * kept_total + 4 * counts.numel()
-        peak_tf = peaks["bf16_tflops"]
-        achieved_tf = flops / (att_ms * 1e-3) / 1e12
-        roofline = {"kernel": "sparse_attn64_kernel" if pq == 64 else "sparse_attn_kernel", "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf,
-                    "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
-                    "traffic": (NCU_TRAFFIC_BYTES.get(wl.name) or
-                                (NCU_TRAFFIC_PER_HEAD_32K * wl.heads if wl.name == "c2" else None)),
-                    "traffic_note": "ncu capture of 8 heads (c2h8), scaled by heads" if wl.name == "c2" else None,
-                    "peak_source": peaks["_source"] + " burst"}
-        sel_gbs = sel_bytes / ((t_pool + sel_ms) * 1e-3) / 1e9
-        roofline_select = {"kernel": "pool_q_kernel+select_kernel", "bound": "hbm", "achieved": sel_gbs,
-                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"],
-                           "algorithmic_bytes": sel_bytes, "peak_source": peaks["_source"]}
-
-        # ---- dense attention on the same GPU, for context (library kernel, one head group) ----
-        dense_ms = None
-        try:
-            hd = min(wl.heads, 4)
-            rep = wl.heads // wl.kv_heads
-            qd = wl.q[:, :hd]
-            kd = wl.k[:, : max(1, hd // rep)].repeat_interleave(min(rep, hd), dim=1)[:, :hd]
-            vd = wl.v[:, : max(1, hd // rep)].repeat_interleave(min(rep, hd), dim=1)[:, :hd]
-            f = lambda: torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, is_causal=wl.causal)
-            dense_ms = time_cuda(f, 1, 3) * wl.heads / hd
-        except Exception:  # the comparison is optional
-            dense_ms = None
-
-        # ---- CPU baseline: the oracle on a bounded sample, host cores of this box ----
-        cores = os.cpu_count() or 1
-        torch.set_num_threads(cores)
-        cwl, q_rows = cpu_sample(args.workload, thr, args.cpu_tiles)
-        run_cpu_sample(cwl, q_rows, thr)
-        reps, secs, cflops = 0, 0.0, 0.0
-        while secs < 10.0 and reps < 1000:
-            dt, cflops = run_cpu_sample(cwl, q_rows, thr)
-            secs += dt
-            reps += 1
-        cpu_value = cflops * reps / secs / 1e12
-        cpu_baseline = {"value": cpu_value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                        "sample": f"1 head x {q_rows.shape[2] // pq} query tiles x all {wl.seq_len} keys of "
-                                  f"{wl.name}, {reps} passes, {secs:.1f} s"}
-
-        line = {
-            "metric": "vecattention_prefill_effective_tflops", "value": value, "unit": "TFLOP/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic",
-            "config": {"workload": wl.name, "batch": wl.batch, "heads": wl.heads, "kv_heads": wl.kv_heads,
-                       "seq_len": wl.seq_len, "head_dim": D, "causal": wl.causal, "q_pooling_size": pq,
-                       "k_local_size": bk, "group_k_block": g, "chunk_size": chunk, "threshold": thr,
-                       "keep_ratio": kept, "effective_flops_per_step_per_gpu": flops,
-                       "l2": "inputs larger than L2 (q+k+v = %.0f MB per GPU), no flush" %
-                             ((wl.q.numel() + 2 * wl.k.numel()) * esz / 1e6),
-                       "parallelism": ("replicated workload per GPU" if args.scaling == "weak" else "heads sharded")},
-            "ms_per_layer": ms_step, "stage_ms": stage, "dense_attention_ms": dense_ms,
-            "roofline": roofline, "roofline_select": roofline_select, "cpu_baseline": cpu_baseline,
-            "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-        }
-    barrier()
+    # ---- combine the ranks, then leave the process group: everything below is rank 0's own work and must not
+    # keep the other ranks spinning in a collective ----
+    local = torch.tensor([ms_total, e2e_ms, e2e_err, float(status.item()), flops, float(h2d), float(d2h), kept_pairs,
+                          float(wl.eligible_pairs_per_head() * wl.heads * wl.batch)], dtype=torch.float64, device=dev)
     if world > 1:
+        mx, sm = local.clone(), local.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        per_rank = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(per_rank, local)
+        barrier()
         dist.destroy_process_group()
-    if line is not None:
+    else:
+        mx = sm = local
+        per_rank = [local]
+    if int(mx[3]) != 0:
+        raise RuntimeError(f"a kernel reported status {int(mx[3])} (1 = index overflow, 2 = internal wait timeout) during the timed region")
+    if rank != 0:
+        return
+    ms_step = float(mx[0]) / args.steps
+    flops_all = float(sm[4])
+    value = flops_all / (ms_step * 1e-3) / 1e12
+    kept = float(sm[7]) / float(sm[8])
+    heads_total = cfg["heads"] if strong else wl.heads
+    config = {"workload": wl.name, "batch": wl.batch, "heads": heads_total, "kv_heads": cfg["kv_heads"] if strong else wl.kv_heads,
+              "heads_per_gpu": wl.heads, "seq_len": wl.seq_len, "head_dim": D, "causal": wl.causal, "q_pooling_size": pq,
+              "k_local_size": bk, "group_k_block": g, "chunk_size": chunk, "threshold": thr, "keep_ratio": kept,
+              "effective_flops_per_step": flops_all,
+              "l2": "inputs larger than L2 (q+k+v = %.0f MB per GPU), no flush" % ((wl.q.numel() + 2 * wl.k.numel()) * 2 / 1e6),
+              "parallelism": ("heads sharded, no collective on the path" if strong else "replicated workload per GPU")}
+    line = {"metric": "vecattention_prefill_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+            "ms_per_layer": ms_step, "gpu_launches": launches, "clocks": clocks, "status_word": 0,
+            "rank_ms_per_step": [float(r[0]) / args.steps for r in per_rank]}
+    if args.profile_window:
+        line["note"] = "profile window run: per-kernel, end-to-end and CPU legs skipped"
         print(json.dumps(line), flush=True)
+        return
+    line["e2e"] = {"value": flops_all / (float(mx[1]) * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": float(mx[1]),
+                   "h2d_bytes_per_step": int(sm[5]), "d2h_bytes_per_step": int(sm[6]),
+                   "max_abs_diff_vs_device_call": float(mx[2]),
+                   "note": "VecAttention_prefill_host on every rank at once: pinned host q/k/v in, pinned host output out, "
+                           "head slices pipelined over three streams; device time, max over ranks"}
+
+    # ---- rank 0 only from here on ----
+    peaks = load_peaks()
+    stage = _stage_times(va, api, wl, thr, counts, bcnt, bidx, out)
+    roofline, roofline_select = _rooflines(wl, peaks, stage, flops, counts)
+    dense_ms, dense_which, dense_tried = _dense_baseline(wl)
+    ref_sel_ms, ref_sel_note = _reference_triton_select_ms(wl, thr)
+    line.update({"stage_ms": stage, "roofline": roofline, "roofline_select": roofline_select,
+                 "dense_attention_ms": dense_ms,
+                 "dense_attention": {"ms_this_gpus_heads": dense_ms, "kernel": dense_which, "tried_ms": dense_tried,
+                                     "note": "four heads timed, scaled to this GPU's heads"},
+                 "reference_triton_select_ms": ref_sel_ms,
+                 "reference_triton_select": {"ms": ref_sel_ms, "note": ref_sel_note,
+                                             "ours_ms": stage["pool_ms"] + stage["select_ms"]}})
+
+    # ---- CPU baseline: the oracle on a bounded sample, host cores of this box; its result also checks the GPU ----
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cwl, q_rows = cpu_sample(args.workload, thr, args.cpu_tiles)
+    _, _, ref_out, ref_counts = run_cpu_sample(cwl, q_rows, thr, keep=True)
+    line["parity"] = _parity_on_cpu_sample(va, cwl, q_rows, thr, ref_out, ref_counts, dev)
+    reps, secs, cflops = 0, 0.0, 0.0
+    while secs < 10.0 and reps < 1000:
+        dt, cflops = run_cpu_sample(cwl, q_rows, thr)
+        secs += dt
+        reps += 1
+    line["cpu_baseline"] = {"value": cflops * reps / secs / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                            "sample": f"1 head x {q_rows.shape[2] // pq} query tiles x all {cwl.seq_len} keys of "
+                                      f"{cwl.name}, {reps} passes, {secs:.1f} s"}
+    del cwl, q_rows, ref_out
+
+    # ---- the other configurations in brief (one GPU only): the same measurement with fewer steps ----
+    if world == 1 and args.others:
+        others = {}
+        del wl, out, counts, bcnt, bidx
+        torch.cuda.empty_cache()
+        for name in [w for w in ("c2", "c3", "c4", "c5") if w != args.workload]:
+            owl = make_workload(name, device=dev)
+            othr = _calibrated_threshold(va, owl, args)
+            oout = torch.empty_like(owl.q)
+            _, ocnt = va.VecAttention_prefill(owl.q, owl.k, owl.v, othr, owl.q_pooling_size, owl.k_local_size,
+                                              owl.group_k_block, owl.causal, owl.chunk_size, return_selection=True)
+            obc, obi = api.block_tables(owl.batch, owl.heads, owl.seq_len, owl.q_pooling_size, owl.causal, dev)
+            oflops = effective_flops(ocnt, owl, obc if owl.causal else None)
+            oargs = argparse.Namespace(**{**vars(args), "steps": 3, "warmup": 3})
+            oms = _measure(va, api, owl, othr, oargs, barrier, status, oout) / 3
+            ostage = _stage_times(va, api, owl, othr, ocnt, obc, obi, oout)
+            orf, ors = _rooflines(owl, peaks, ostage, oflops, ocnt)
+            others[name] = {"ms_per_layer": oms, "effective_tflops": oflops / (oms * 1e-3) / 1e12, "threshold": othr,
+                            "keep_ratio": float(ocnt.sum()) / (owl.eligible_pairs_per_head() * owl.heads * owl.batch),
+                            "stage_ms": ostage, "roofline_frac": orf["frac"], "roofline_select_frac": ors["frac"]}
+            del owl, oout, ocnt, obc, obi
+            torch.cuda.empty_cache()
+        if int(status.item()) != 0:
+            raise RuntimeError(f"a kernel reported status {int(status.item())}")
+        line["other_workloads"] = others
+    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -457,10 +588,12 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="graft", choices=["graft", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "c2h8", "mini"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--workload", default="c4", choices=["c2", "c3", "c4", "c5", "c2h8", "mini"])
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--threshold", type=float, default=0.0, help="skip calibration and use this MinP threshold")
     ap.add_argument("--cpu-tiles", type=int, default=512, help="query tiles in the bounded CPU sample")
+    ap.add_argument("--no-others", dest="others", action="store_false",
+                    help="skip the brief measurement of the other configurations (one-GPU runs only)")
     ap.add_argument("--profile-window", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for `ncu --profile-from-start off`) "
                          "and skip the per-kernel, end-to-end and CPU legs")
