@@ -253,6 +253,7 @@ def _stage_times(va, api, wl, thr, counts, bcnt, bidx, out):
     free, _ = torch.cuda.mem_get_info()
     step_rows = wl.seq_len if idx_all <= min(32 << 30, int(free * 0.4)) else chunk
     sel_ms = att_ms = 0.0
+    overlap = None
     gap = -math.log(thr + 1e-9)
     for i in range(0, wl.seq_len, step_rows):
         t0, t1 = i // pq, min(wl.nq, -(-(i + step_rows) // pq))
@@ -267,8 +268,29 @@ def _stage_times(va, api, wl, thr, counts, bcnt, bidx, out):
         att = lambda: api._sparse_attn_bhsd(qc, wl.k[:, :, :sk_eff], wl.v[:, :, :sk_eff], pq, bc, bi, cc, ci,
                                             wl.causal, q_offset=i, out=oc)
         att_ms += time_cuda(att, 2, 5)
+        if i == 0:
+            overlap = _adjacent_tile_overlap(cc, ci, wl.seq_len)
         del cc, ci
-    return {"pool_ms": t_pool, "select_ms": sel_ms, "attn_ms": att_ms}
+    return {"pool_ms": t_pool, "select_ms": sel_ms, "attn_ms": att_ms, "adjacent_tile_union_over_mean": overlap}
+
+
+def _adjacent_tile_overlap(cc, ci, sk, pairs=64):
+    """How far the selected-column lists of neighbouring query tiles coincide: |A union B| / mean(|A|, |B|) over a
+    sample of adjacent tile pairs of the first head (1 = identical lists, 2 = disjoint).  It bounds what sharing
+    one gathered key set between two tiles could save."""
+    nq = cc.shape[2]
+    if nq < 2:
+        return None
+    tiles = torch.linspace(0, nq - 2, min(pairs, nq - 1)).long().unique().tolist()
+    union = mean = 0.0
+    for t in tiles:
+        m = torch.zeros(2, sk + 1, dtype=torch.bool, device=ci.device)
+        for j in range(2):
+            n = int(cc[0, 0, t + j])
+            m[j, ci[0, 0, t + j, :n].long()] = True
+        union += float((m[0] | m[1]).sum())
+        mean += float(m.sum()) / 2
+    return union / max(mean, 1.0)
 
 
 def _rooflines(wl, peaks, stage, flops, counts):

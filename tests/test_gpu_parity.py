@@ -370,3 +370,41 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable(va):
     ref = O.vecattention_prefill(q, k, k, 0.5, 64, 16, 16, False, 512)
     assert int(status.item()) == 0
     assert (out.float().cpu() - ref.float()).abs().max() <= MAX_ABS
+
+
+# ---------------------------------------------------------------------------------------------
+def test_dispatcher_with_config(va, tmp_path):
+    """customize_prefill_attention: per-layer threshold tensor, vision positions from the configuration, the
+    dense method on the same kernel, the latency record and the Q/K dump."""
+    import types
+    from vecattention_b200.dispatch import SPARSITY_RECORD
+    b, h, hkv, s = 1, 4, 2, 1500
+    q = _rand((b, h, s, 128), 81, torch.bfloat16).cuda()
+    k = _rand((b, hkv, s, 128), 82, torch.bfloat16).cuda()
+    v = _rand((b, hkv, s, 128), 83, torch.bfloat16).cuda()
+    layer = types.SimpleNamespace(layer_idx=1)
+    thr = torch.tensor([[0.3] * h, [0.6, 0.7, 0.8, 0.9], [0.9] * h], device="cuda")   # (layers, heads)
+    cfg = va.FastPrefillConfig(metric="vecattention", threshold=thr, group_k_block=16, chunk_size=1024,
+                               vision_start_position=100, vision_end_position=1300, dump_qk_dir=str(tmp_path))
+    SPARSITY_RECORD.attention_latency_list = []
+    got = va.customize_prefill_attention(layer, q, k, v, config=cfg)
+    want = va.VecAttention_prefill_vision(q, k, v, thr[1], 64, 16, 16, True, 1024, vision_start_position=100,
+                                          vision_end_position=1300)
+    assert torch.equal(got, want)
+    one = va.VecAttention_prefill(q, k, v, torch.tensor(0.7, device="cuda"), 64, 16, 16, True, 1024)   # a 0-d tensor
+    assert torch.equal(one, va.VecAttention_prefill(q, k, v, torch.full((h,), 0.7, device="cuda"), 64, 16, 16, True, 1024))
+    assert len(SPARSITY_RECORD.attention_latency_list) == 1
+    torch.cuda.synchronize()
+    e0, e1 = SPARSITY_RECORD.attention_latency_list[0]
+    assert e0.elapsed_time(e1) > 0
+    assert (tmp_path / "input" / "layer_1_qk.pt").exists()
+    kk, vv = k.repeat_interleave(2, dim=1), v.repeat_interleave(2, dim=1)
+    for causal in (True, False):
+        dense = va.customize_prefill_attention(layer, q, k, v, causal=causal, config=va.FastPrefillConfig(metric="full"))
+        ref = torch.nn.functional.scaled_dot_product_attention(q, kk, vv, is_causal=causal)
+        err = (dense.float() - ref.float()).abs()
+        assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS, (causal, err.max().item())
+    with pytest.raises(NotImplementedError):
+        va.customize_prefill_attention(layer, q, k, v, config=va.FastPrefillConfig(metric="anchor"))
+    with pytest.raises(AssertionError):
+        va.customize_prefill_attention(layer, q, k, v, causal=False, config=va.FastPrefillConfig(metric="flex"))

@@ -238,3 +238,30 @@ def test_stage_workspace_queries(lib):
     n = C.c_size_t(123)
     assert lib.lib().va_sparse_attn_workspace_bytes(C.byref(lib.AttnArgs()), C.byref(n)) == 0 and n.value == 0
     assert lib.lib().va_select_workspace_bytes(None, C.byref(n)) == -1
+
+
+def test_fastprefill_config_and_flags(built_library):
+    """The caller-side configuration object and its command-line flags, with the reference's names and
+    defaults (spattn/src/models/config_args.py)."""
+    import argparse
+    from vecattention_b200 import (FastPrefillConfig, add_fastprefill_args, build_output_file_from_config,
+                                   get_fastprefill_config)
+    c = FastPrefillConfig()
+    assert (c.metric, c.block_size_q, c.block_size_k, c.group_k_block, c.chunk_size) == ("xattn", 64, 16, 1, 8192)
+    assert c.vision_start_position is None and c.output_time is True and c.input_id == "input"
+    assert not hasattr(c, "threshold") and "threshold" not in c       # only present when given
+    c = FastPrefillConfig(metric="vecattention", threshold=0.8, group_k_block=16)
+    assert c.threshold == 0.8 and c["group_k_block"] == 16 and isinstance(c, dict)
+    c.vision_end_position = 100
+    assert c["vision_end_position"] == 100
+    with pytest.raises(TypeError):
+        FastPrefillConfig(no_such_field=1)
+    ap = add_fastprefill_args(argparse.ArgumentParser())
+    ns = ap.parse_args([])
+    assert (ns.fastprefill_metric, ns.fastprefill_threshold, ns.fastprefill_chunk_size) == ("full", 0.9, 65536)
+    ns = ap.parse_args("--fastprefill-metric vecattention --fastprefill-threshold 0.7 --fastprefill-group-k-block 8192 "
+                       "--fastprefill-block-size-k 16 --fastprefill-chunk-size 32768".split())
+    c = get_fastprefill_config(ns)
+    assert (c.metric, c.threshold, c.group_k_block, c.chunk_size, c.input_id) == ("vecattention", 0.7, 8192, 32768, "input")
+    assert build_output_file_from_config("out/res.json", c) == "out/res_metric=vecattention_th=0.7_qps=64_kls=16_gkb=8192.json"
+    assert build_output_file_from_config("r.txt", FastPrefillConfig(metric="full")) == "r_metric=full.txt"

@@ -54,3 +54,60 @@ def test_two_rank_head_sharding_equals_single_rank(heads, kv_heads):
     results = mgr.dict()
     mp.spawn(_worker, args=(2, port, heads, kv_heads, results), nprocs=2, join=True)
     assert results[0] and results[1]
+
+
+# ---------------------------------------------------------------------------------------------
+# A rank that fails before the gather: the others learn of it on the host and nobody hangs.
+# ---------------------------------------------------------------------------------------------
+def _failing_worker(rank, world, port, mode, results):
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    from oracle import vecattn_oracle as O
+    from vecattention_b200.sharding import ShardFailure, prefill_head_sharded
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(1, 2, 192, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, 2, 192, 128, generator=g).to(torch.bfloat16)
+    hs, ks = local_slices(2, 2, rank, world)
+
+    def prefill(*a, **kw):
+        if rank == 1 and mode == "raises":
+            raise ValueError("injected failure on rank 1")
+        return O.vecattention_prefill(*a, **kw)
+    dist.barrier()
+    if rank == 1 and mode == "exits":
+        os._exit(3)   # the process is gone before the exchange: no goodbye to the group
+    try:
+        prefill_head_sharded(q[:, hs], k[:, ks], k[:, ks], 0.5, 64, 16, 4, True, 128, total_heads=2, total_kv_heads=2,
+                             prefill_fn=prefill)
+        results[rank] = "no error"
+    except ShardFailure as e:
+        results[rank] = f"ShardFailure {e.ranks}"
+    except Exception as e:  # noqa: BLE001 - the process group's own error for a vanished peer
+        results[rank] = f"group error {type(e).__name__}"
+    os._exit(0)   # skip the group's teardown: the peer may be gone
+
+
+@pytest.mark.parametrize("mode", ["raises", "exits"])
+def test_failed_rank_is_reported_to_the_others_without_a_hang(mode):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    mgr = ctx.Manager()
+    results = mgr.dict()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, mode, results)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(timeout=90)
+    alive = [pr.is_alive() for pr in procs]
+    for pr in procs:
+        if pr.is_alive():
+            pr.kill()
+    assert not any(alive), "a rank hung after its peer failed"
+    if mode == "raises":
+        assert results[0] == "ShardFailure [1]" and results[1] == "ShardFailure [1]", dict(results)
+    else:
+        assert procs[1].exitcode == 3
+        assert results[0].startswith("group error") or results[0].startswith("ShardFailure"), dict(results)

@@ -9,7 +9,9 @@ key tail differently):
   * the selection of ``fuse_qk_softmax_minp_wo_causal`` (spattn/src/kernels/vecattention_kernels.py:
     59-181, kernels :206-345) in bf16 at the sizes of benchmark configurations 2-5 (one KV group, all
     query tiles, the operator's chunk loop), with a key length that is not a multiple of the key
-    block (NaN-padded tail, :117-127), with per-head gaps (the second kernel) and in fp16.
+    block (NaN-padded tail, :117-127), with per-head gaps (the second kernel) and in fp16;
+  * the recall / sparsity measure of the threshold tuner, ``seg_pr_perHead``
+    (spattn/threshold/model_tuner.py:118-226), against ``recall.selection_recall_sparsity``.
 
 Both selections are given the reference's pooled queries, so the comparison isolates the selection
 rule; sets must be equal except keys whose estimate lies within 1e-6 of the keep/drop boundary (the
@@ -175,3 +177,23 @@ def test_reference_triton_selection_edge_cases(va, ref, cfg):
     else:
         gap = -math.log(0.6 + 1e-9)
     _compare_selection(va, ref, theirs, k, gap, cfg["causal"], 64, 16, cfg["g"], 65536 // 64, str(cfg))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_reference_tuner_recall_and_sparsity(va, ref, causal):
+    """The tuner's own ``seg_pr_perHead`` (dense softmax times the selection mask, in the input dtype) against
+    the log-sum-exp route of this package.  The reference accumulates in bf16 (per-row recalls, the per-head
+    sums and the sparsity), hence the tolerances."""
+    from spattn.threshold.model_tuner import seg_pr_perHead
+    from vecattention_b200.recall import selection_recall_sparsity
+    h, s = 4, 1100
+    q = _rand((1, h, s, 128), 91, torch.bfloat16)
+    k = _rand((1, h, s, 128), 92, torch.bfloat16)
+    k[:, :, ::17] *= 3.0
+    thr = torch.tensor([0.3, 0.5, 0.7, 0.9], device="cuda")
+    ref_recall, ref_sparsity = seg_pr_perHead(q, k, 64, 16, 16, thr, 512, causal)
+    recall, sparsity = selection_recall_sparsity(q, k, 64, 16, 16, thr, 512, causal)
+    print(f"causal={causal}: recall reference {ref_recall.float().tolist()} ours {recall.tolist()}; "
+          f"sparsity reference {ref_sparsity.float().tolist()} ours {sparsity.tolist()}")
+    assert (recall - ref_recall.float()).abs().max() <= 6e-3
+    assert (sparsity - ref_sparsity.float()).abs().max() <= 1.5e-2

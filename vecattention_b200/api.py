@@ -73,6 +73,8 @@ def _gap_args(gap: Union[float, torch.Tensor], batch: int, heads: int, device) -
     """float gap -> (gap, None, 0); tensor gap -> (0, fp32 device tensor, batch stride)."""
     if isinstance(gap, torch.Tensor):
         g = gap.to(device=device, dtype=torch.float32).contiguous().reshape(-1)
+        if g.numel() == 1:  # one value for all heads, given as a tensor
+            g = g.expand(heads).contiguous()
         if g.numel() == heads:
             return 0.0, g, 0
         if g.numel() == batch * heads:
