@@ -36,10 +36,13 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu
 # capture summarised under profiles/ (workload -> bytes); None until a capture exists
-NCU_TRAFFIC_BYTES = {"c2h8": 305.3e6}  # profiles/sparse_attn64_kernel_c2h8.md
+# workload -> bytes; c4 was captured at full size (one-pass metrics): profiles/launch_list_c4.md
+NCU_TRAFFIC_BYTES = {"c2h8": 303.9e6, "c4": 6.24e9 + 0.726e9}  # profiles/sparse_attn64_kernel_c2h8.md
+NCU_SELECT_TRAFFIC_BYTES = {"c4": (729.9e6 + 12.9e6) + (810.9e6 + 649.6e6) + (670.3e6 + 1.71e9)}  # pool + mask + expand
 # the capture is of 8 heads; DRAM traffic of this kernel grows in proportion to the heads processed
-NCU_TRAFFIC_PER_HEAD_32K = 305.3e6 / 8
+NCU_TRAFFIC_PER_HEAD_32K = 303.9e6 / 8
 D = 128
+CONFIG_HEADS = {"c2": 32, "c3": 40, "c4": 24, "c5": 28, "c2h8": 8}
 
 
 def load_peaks():
@@ -298,19 +301,23 @@ def _rooflines(wl, peaks, stage, flops, counts):
     kept_total = float(counts.sum())
     sel_bytes = (wl.q.numel() + wl.k.numel()) * esz + 4 * kept_total + 4 * counts.numel()
     achieved_tf = flops / (stage["attn_ms"] * 1e-3) / 1e12
-    traffic = NCU_TRAFFIC_PER_HEAD_32K * wl.heads if wl.name in ("c2", "c2h8") else None
+    full = wl.heads == CONFIG_HEADS.get(wl.name)
+    traffic = (NCU_TRAFFIC_PER_HEAD_32K * wl.heads if wl.name in ("c2", "c2h8") else
+               NCU_TRAFFIC_BYTES.get(wl.name) if full else None)
     roofline = {"kernel": "sparse_attn64_kernel" if wl.q_pooling_size == 64 else "sparse_attn_kernel", "bound": "tensor",
                 "achieved": achieved_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved_tf / peaks["bf16_tflops"], "traffic": traffic,
-                "traffic_note": ("ncu capture of 8 heads x 32 K tokens, scaled by heads" if traffic else
-                                 "captured on the 8-head 32 K case only (profiles/); DRAM traffic there equals the "
-                                 "algorithmic bytes"),
+                "traffic_note": ("ncu capture of 8 heads x 32 K tokens, scaled by heads" if wl.name in ("c2", "c2h8") else
+                                 "one-pass ncu capture of this workload at full size (profiles/launch_list_c4.md): 1.5x the "
+                                 "algorithmic 4.6 GB, K/V of two 61 MB heads do not both stay in the 126 MB L2" if traffic else
+                                 "not captured for this workload or head count"),
                 "peak_source": peaks["_source"] + " burst"}
     sel_gbs = sel_bytes / ((stage["pool_ms"] + stage["select_ms"]) * 1e-3) / 1e9
     est_flops = 2.0 * wl.nq * wl.seq_len * D * wl.heads * wl.batch * (0.5 if wl.causal else 1.0)
     roofline_select = {"kernel": "pool_q_kernel+select_mask_kernel+select_expand_kernel", "bound": "hbm", "achieved": sel_gbs,
                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": sel_gbs / peaks["hbm_gbs"],
                        "algorithmic_bytes": sel_bytes, "peak_source": peaks["_source"],
+                       "traffic": NCU_SELECT_TRAFFIC_BYTES.get(wl.name) if full else None,
                        "estimate_tflops": est_flops / (stage["select_ms"] * 1e-3) / 1e12,
                        "estimate_frac_of_tensor_peak": est_flops / (stage["select_ms"] * 1e-3) / 1e12 / peaks["bf16_tflops"]}
     return roofline, roofline_select
@@ -581,7 +588,7 @@ def graft_arm(args):
         others = {}
         del wl, out, counts, bcnt, bidx
         torch.cuda.empty_cache()
-        for name in [w for w in ("c2", "c3", "c4", "c5") if w != args.workload]:
+        for name in [w for w in ("c2", "c3", "c4", "c5", "d128") if w != args.workload]:
             owl = make_workload(name, device=dev)
             othr = _calibrated_threshold(va, owl, args)
             oout = torch.empty_like(owl.q)
@@ -610,7 +617,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="graft", choices=["graft", "reference"])
-    ap.add_argument("--workload", default="c4", choices=["c2", "c3", "c4", "c5", "c2h8", "mini"])
+    ap.add_argument("--workload", default="c4", choices=["c2", "c3", "c4", "c5", "d128", "c2h8", "mini"])
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--threshold", type=float, default=0.0, help="skip calibration and use this MinP threshold")
     ap.add_argument("--cpu-tiles", type=int, default=512, help="query tiles in the bounded CPU sample")

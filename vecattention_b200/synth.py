@@ -65,6 +65,10 @@ CONFIGS = {
     # config 5: Qwen2.5-VL-style GQA long-video prefill, causal
     "c5": dict(batch=1, heads=28, kv_heads=4, seq_len=65536, causal=True, keep=0.10, seed=4,
                stripe_frac=0.01, sigma=1.0, sink=4, group_k_block=16, chunk_size=65536),
+    # the reference's default arguments (q_pooling_size 128, k_local_size 128, group_k_block 1, causal, chunks of
+    # 16 K rows; spattn/src/VecAttention.py:14-18) on the quick-use shape
+    "d128": dict(batch=1, heads=32, kv_heads=32, seq_len=32768, causal=True, keep=0.10, seed=1,
+                 stripe_frac=0.01, sigma=1.0, q_pooling_size=128, k_local_size=128, group_k_block=1, chunk_size=16384),
     # 8 heads of config 2: inputs above the L2 size, small enough for a profiler capture
     "c2h8": dict(batch=1, heads=8, kv_heads=8, seq_len=32768, causal=False, keep=0.10, seed=1,
                  stripe_frac=0.01, sigma=1.0, group_k_block=16, chunk_size=32768),
