@@ -1,0 +1,405 @@
+// Vector-sparse flash attention for q_pooling_size 128 on tcgen05 MMAs with M = 128.
+//
+// One CTA per query tile of 128 rows; keys are taken 128 at a time from the tile's dense 64-key
+// blocks and then from its selected-column list (row gather).  S = Q K^T and O += P V are plain
+// tcgen05.mma with M = 128, N = 128: accumulator row r lives in TMEM lane r.  A 128-row tile reads
+// every gathered key row for twice as many query rows as a 64-row tile, which is what this path is
+// bound by (shared-memory traffic per FLOP).
+//
+// Warp roles (576 threads, one CTA per SM):
+//   warps 0-7  softmax: all eight work on the same chunk; thread (w, lane) owns half a row, row
+//              (w % 4) * 32 + lane (the TMEM lanes warp w can reach), keys (w / 4) * 64 .. + 63 of the
+//              chunk.  Per chunk it pulls its 64 scores into registers (which frees the S buffer),
+//              forms the row maximum with the row's other owner through shared memory, raises the
+//              running maximum lazily (only when a chunk exceeds it by more than 2^8), writes
+//              P = exp2(S*scale - m) in the input dtype into the P operand tile once the previous
+//              chunk's PV product has read it, and rescales its half of the row of O in the rare
+//              chunks where the maximum moved.
+//   warps 8-11  K gather producers, warps 12-15 V gather producers: cp.async 16-byte pieces of the
+//              selected rows into rings of 128-byte-swizzled operand tiles (2 stages each).
+//   warps 16,17  MMA issuers (one thread each): warp 16 issues S_j = Q K_j^T into one of two S
+//              buffers, warp 17 issues O += P_j V_j; the tensor pipe works on S_{j+1} while the
+//              softmax of chunk j runs.
+// The producer warpgroups give registers to the softmax warpgroups (setmaxnreg).
+// Every wait is a bounded mbarrier wait; a timeout sets VA_STATUS_TIMEOUT and unwinds the CTA.
+#include "va_common.cuh"
+#include "va_sm100.cuh"
+#include "va_attn.cuh"
+
+namespace va {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int kChunk = 128;
+constexpr int kTileBytes = 128 * 256;  // 128 rows of 256 bytes: Q, P, one K or V stage
+constexpr int kKStages = 2;
+constexpr int kVStages = 2;
+constexpr int kThreads = 576;
+// Registers per thread: launched with 96; the two producer warpgroups hand 40 each back and the two softmax
+// warpgroups take them: 256 * 56 + 256 * 136 + 64 * 96 = 576 * 96.
+constexpr int kProducerRegs = 56, kSoftmaxRegs = 136;
+constexpr size_t kSmem = 1024 + (size_t)kTileBytes * (2 + kKStages + kVStages);  // Q, P, K ring, V ring
+constexpr float kRescaleThreshold = 8.0f;                                        // log2 units
+
+struct Barriers {
+  uint64_t qfull, kfull[kKStages], kempty[kKStages], vfull[kVStages], vempty[kVStages];
+  uint64_t sfull[2], sempty[2], pfull, pempty, ofull, xch[4], fin;
+};
+
+template <int N>
+__device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 1) sparse_attn128_kernel(const AttnParams p) {
+  using T = typename Elem<DT>::T;
+  constexpr int PQ = 128;
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ Barriers bars;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int keys_s[8][kChunk];           // ring deep enough that a slot is rewritten long after its last reader
+  __shared__ __align__(16) int mask_s[8][4];  // per chunk and K producer warp: does any of its keys need masking?
+  __shared__ float xch_s[2][256];             // [phase][half * 128 + row]: chunk maxima swapped by a row's two owners
+  __shared__ float fin_s[256];                // [half * 128 + row]: row sums, added in the epilogue
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // causal tiles grow with their index: the longest are started first, so the grid's tail is made of short ones
+  const int tile = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / p.rep;
+  const int row0 = tile * PQ;
+  const int64_t trow = ((int64_t)b * p.heads + h) * p.nq + tile;
+  const int nblk = p.blk_count ? __ldg(p.blk_count + trow) : 0;
+  const int ncol = __ldg(p.col_count + trow);
+  const int nslots = nblk * 64 + ncol;
+  const int nchunks = (nslots + kChunk - 1) / kChunk;
+  T* ob = static_cast<T*>(p.out) + b * p.o_sb + h * p.o_sh;
+
+  if (nchunks == 0) {  // no key at all: the tile's output is zero
+    for (int i = tid; i < PQ * 16; i += kThreads) {
+      const int r = i >> 4, c = i & 15;
+      if (row0 + r < p.sq) *reinterpret_cast<uint4*>(ob + (int64_t)(row0 + r) * p.o_ss + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+    if (p.lse && tid < PQ && row0 + tid < p.sq) p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + tid] = -INFINITY;
+    return;
+  }
+
+  unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+  unsigned char* q_s = smem;
+  unsigned char* p_s = smem + kTileBytes;
+  unsigned char* k_s = smem + 2 * kTileBytes;                 // K ring
+  unsigned char* v_s = k_s + (size_t)kKStages * kTileBytes;   // V ring
+
+  if (tid == 0) {
+    mbar_init(&bars.qfull, 256);  // per producer thread: one asynchronous copy-completion arrival + one plain arrival
+    for (int s = 0; s < kKStages; ++s) {
+      mbar_init(&bars.kfull[s], 256);
+      mbar_init(&bars.kempty[s], 1);
+    }
+    for (int s = 0; s < kVStages; ++s) {
+      mbar_init(&bars.vfull[s], 256);
+      mbar_init(&bars.vempty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars.sfull[s], 1);
+      mbar_init(&bars.sempty[s], 256);
+    }
+    mbar_init(&bars.pfull, 256);
+    mbar_init(&bars.pempty, 1);
+    for (int s = 0; s < 4; ++s) mbar_init(&bars.xch[s], 64);
+    mbar_init(&bars.fin, 256);
+    mbar_init(&bars.ofull, 1);
+    fence_proxy_async();
+  }
+  if (warp == 16) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t t_s0 = tmem, t_o = tmem + 256;  // S buffers at columns 0 and 128, O at 256 (128 columns each)
+
+  bool timed_out = false;
+
+  if (warp >= 8 && warp < 16) {
+    // ======================= gather producers (warps 8-11: K and the Q tile, warps 12-15: V) =======================
+    reg_dealloc<kProducerRegs>();
+    const bool is_v = warp >= 12;
+    const int pt = is_v ? tid - 384 : tid - 256;
+    const T* qb = static_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
+    const T* kb = static_cast<const T*>(p.k) + b * p.k_sb + hkv * p.k_sh;
+    const T* vb = static_cast<const T*>(p.v) + b * p.v_sb + hkv * p.v_sh;
+    const int32_t* blk = p.blk_idx + trow * p.blk_stride;
+    const int32_t* col = p.col_idx + trow * p.col_stride;
+    if (!is_v) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {  // Q tile: rows beyond the sequence are zero
+        const int pce = pt + i * 128, r = pce >> 4, c = pce & 15;
+        const bool ok = row0 + r < p.sq;
+        cp_async16(smem_addr(q_s + tile_off(128, r, c)), qb + (int64_t)(ok ? row0 + r : 0) * p.q_ss + c * 8, ok);
+      }
+      cp_async_arrive_noinc(&bars.qfull);
+      mbar_arrive(&bars.qfull);
+    }
+    // Copy geometry.  A warp covers two key rows per instruction: lanes 0-15 the sixteen 16-byte
+    // pieces of row rbase + 8 i, lanes 16-31 those of the next row.  Because the rows of one thread
+    // differ by multiples of 8, its swizzled piece position is the same in all of them and the
+    // shared-memory destinations are one base address plus i * 1024.
+    // Each lane fetches ONE key index per chunk (that of row rbase + 8 * (lane & 15)), two chunks
+    // ahead; the sixteen indices a thread needs are then exchanged with warp shuffles.
+    const int pw = (pt >> 5), hi = lane >> 4, c = lane & 15;
+    const int rbase = 2 * pw + hi;
+    const uint32_t dst_off = tile_off(128, rbase, c);
+    const int my_slot = rbase + 8 * c;
+    auto fetch_raw = [&](int j) -> int {
+      const int slot = j * kChunk + my_slot;
+      const int ci = min(max(slot - nblk * 64, 0), max(ncol - 1, 0));
+      return ldg_nc(slot < nblk * 64 ? blk + (slot >> 6) : col + ci);
+    };
+    auto decode = [&](int j, int raw) -> int {
+      const int slot = j * kChunk + my_slot;
+      const int key = slot < nblk * 64 ? raw + (slot & 63) : (slot < nslots ? raw : -1);
+      return (key >= 0 && key < p.sk) ? key : -1;
+    };
+    auto spread = [&](int key, int (&out)[16]) {
+      const int kcl = max(key, 0);  // an unused slot copies row 0: its scores are masked and its P is zero
+#pragma unroll
+      for (int i = 0; i < 16; ++i) out[i] = __shfl_sync(0xffffffffu, kcl, (lane & 16) + i);
+    };
+    auto copy_tile = [&](unsigned char* tile_s, const T* base, int64_t stride, const int (&keys)[16], uint64_t* full) {
+      const uint32_t dst = smem_addr(tile_s) + dst_off;
+      const T* src = base + c * 8;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) cp_async16_full(dst + i * 1024, src + (int64_t)keys[i] * stride);
+      cp_async_arrive_noinc(full);
+      mbar_arrive(full);
+    };
+    {
+      int keys[16];
+      int raw0 = fetch_raw(0), raw1 = nchunks > 1 ? fetch_raw(1) : 0;
+      for (int j = 0; j < nchunks && !timed_out; ++j) {
+        const int key = decode(j, raw0);
+        raw0 = raw1;
+        if (j + 2 < nchunks) raw1 = fetch_raw(j + 2);
+        if (!is_v) {
+          keys_s[j & 7][my_slot] = key;
+          // unused slots, and keys that some row of the tile may not see, make the chunk take the masking pass
+          const bool flag = key < 0 || (p.causal && key > p.q_offset + row0);
+          const int any = __any_sync(0xffffffffu, flag);
+          if (lane == 0) mask_s[j & 7][pw] = any;
+        }
+        spread(key, keys);
+        if (!is_v) {
+          const int ks = j % kKStages, ku = j / kKStages;
+          if (!mbar_wait(&bars.kempty[ks], (ku & 1) ^ 1)) { timed_out = true; break; }
+          copy_tile(k_s + (size_t)ks * kTileBytes, kb, p.k_ss, keys, &bars.kfull[ks]);
+        } else {
+          const int vs = j % kVStages, vu = j / kVStages;
+          if (!mbar_wait(&bars.vempty[vs], (vu & 1) ^ 1)) { timed_out = true; break; }
+          copy_tile(v_s + (size_t)vs * kTileBytes, vb, p.v_ss, keys, &bars.vfull[vs]);
+        }
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();  // nothing of this thread may still be in flight when the CTA retires
+  } else if (warp >= 16) {
+    // ======================= MMA issuers =======================
+    if (lane == 0) {
+      constexpr uint32_t in16 = DT == VA_BF16 ? 1u : 0u;
+      bool ok = true;
+      if (warp == 16) {
+        constexpr uint32_t idesc_s = umma_idesc(128, 128, in16, 0, 0);
+        const uint64_t qd = umma_desc(smem_addr(q_s), 16, 1024), kd0 = umma_desc(smem_addr(k_s), 16, 1024);
+        ok = mbar_wait(&bars.qfull, 0);
+        for (int j = 0; j < nchunks && ok; ++j) {
+          const int s = j % kKStages, u = j / kKStages, sb = j & 1, ub = j >> 1;
+          ok = mbar_wait(&bars.kfull[s], u & 1) && mbar_wait(&bars.sempty[sb], (ub & 1) ^ 1);
+          if (!ok) break;
+          fence_proxy_async();  // the producers' cp.async writes (generic proxy) -> visible to the MMA's operand reads
+          tc_fence_after();
+          umma_k128_rows128(t_s0 + (uint32_t)sb * 128, qd, kd0 + (uint64_t)(s * (kTileBytes >> 4)), idesc_s);
+          umma_commit(&bars.kempty[s]);
+          umma_commit(&bars.sfull[sb]);
+        }
+      } else {
+        constexpr uint32_t idesc_pv = umma_idesc(128, 128, in16, 0, 1);
+        const uint32_t p_addr = smem_addr(p_s), vr_addr = smem_addr(v_s);
+        for (int j = 0; j < nchunks && ok; ++j) {
+          const int s = j % kVStages, u = j / kVStages;
+          ok = mbar_wait(&bars.vfull[s], u & 1) && mbar_wait(&bars.pfull, j & 1);
+          if (!ok) break;
+          fence_proxy_async();
+          tc_fence_after();
+          const uint32_t v_addr = vr_addr + (uint32_t)s * kTileBytes;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t poff = (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32;
+            umma(t_o, umma_desc(p_addr + poff, 16, 1024), umma_desc(v_addr + (uint32_t)ks * 16 * 128, 128 * 128, 1024),
+                 idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(&bars.vempty[s]);
+          umma_commit(&bars.pempty);
+          if (j == nchunks - 1) umma_commit(&bars.ofull);
+        }
+      }
+      timed_out = !ok;
+    }
+  } else {
+    // ======================= softmax / correction / epilogue =======================
+    // All eight warps work on the same chunk.  Accumulator row r lives in TMEM lane r; warp w reaches the lane
+    // quarter w % 4, so rows (w % 4) * 32 .. + 31, and takes the key half w / 4 of the chunk: two threads own
+    // half a row each and meet through shared memory.  Both see the same chunk maximum and the same running
+    // maximum, so they take the same decisions without further exchange.
+    reg_alloc<kSoftmaxRegs>();
+    const int half = warp >> 2, qtr = warp & 3;
+    const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
+    const int row = qtr * 32 + lane;
+    const int qpos = p.q_offset + row0 + row;
+    float m_run = -INFINITY, l = 0.f;  // the row's reference maximum (exp2 domain) and this thread's part of the row sum
+    const float sc = p.scale_log2;
+    int xc = 0;
+    for (int j = 0; j < nchunks && !timed_out; ++j) {
+      const int sb = j & 1, ub = j >> 1;
+      const int* keys = keys_s[j & 7] + half * 64;
+      if (!mbar_wait(&bars.sfull[sb], ub & 1)) { timed_out = true; break; }
+      tc_fence_after();
+      const int4 mk = *reinterpret_cast<const int4*>(mask_s[j & 7]);
+      const bool masked = (mk.x | mk.y | mk.z | mk.w) != 0;
+      // ---- this thread's 64 scores -> registers; the S buffer is free again right away ----
+      uint32_t v[64];
+      {
+        uint32_t lo[32], hi[32];
+        tmem_ld32(t_s0 + (uint32_t)sb * 128 + lane_base + half * 64, lo);
+        tmem_ld32(t_s0 + (uint32_t)sb * 128 + lane_base + half * 64 + 32, hi);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v[i] = lo[i];
+          v[32 + i] = hi[i];
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars.sempty[sb]);
+      if (masked) {  // kept out of the arithmetic loops: a branch per element would serialise them
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const int key = keys[i];
+          if (key < 0 || (p.causal && key > qpos)) v[i] = 0xff800000u;  // -inf
+        }
+      }
+      // ---- row maximum of the chunk: own half, then the partner's through shared memory ----
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+      float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      xch_s[xc & 1][half * 128 + row] = mx;
+      mbar_arrive(&bars.xch[qtr]);
+      if (!mbar_wait(&bars.xch[qtr], xc & 1)) { timed_out = true; break; }
+      mx = fmaxf(mx, xch_s[xc & 1][(half ^ 1) * 128 + row]);
+      ++xc;
+      // ---- the row's reference maximum: raised only when this chunk exceeds it by more than the threshold ----
+      const float mx_s = mx * sc;
+      const bool grow = mx_s > m_run + kRescaleThreshold || (m_run == -INFINITY && mx_s > -INFINITY);
+      const float m_new = grow ? mx_s : m_run;
+      const bool rescale = __any_sync(0xffffffffu, grow && j > 0);  // same rows, hence the same outcome, in the partner warp
+      // the P tile is free, and O quiescent, once the PV product of the previous chunk has completed
+      if (j > 0 && !mbar_wait(&bars.pempty, (j - 1) & 1)) { timed_out = true; break; }
+      if (rescale) {
+        tc_fence_after();
+        const float alpha = grow ? ex2_approx(m_run - m_new) : 1.f;  // 2^-inf = 0 when nothing was accumulated yet
+#pragma unroll 1
+        for (int qd = 0; qd < 2; ++qd) {
+          uint32_t o[32];
+          tmem_ld32(t_o + lane_base + half * 64 + qd * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(t_o + lane_base + half * 64 + qd * 32, o);
+        }
+        tmem_wait_st();
+      }
+      if (grow) l *= ex2_approx(m_run - m_new);  // l == 0 while m_run == -inf
+      m_run = m_new;
+      const float mref = m_new == -INFINITY ? 0.f : m_new;
+      // ---- P = exp2(S * scale - m), row sum, P -> shared memory (K-major operand, this thread's 64 keys) ----
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + e * 2]), sc, -mref));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + e * 2 + 1]), sc, -mref));
+          l0 += p0;
+          l1 += p1;
+          pk[e] = Elem<DT>::pack(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(p_s + tile_off(128, row, half * 8 + c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l += l0 + l1;
+      tc_fence_before();
+      fence_proxy_async();
+      mbar_arrive(&bars.pfull);
+    }
+    // ---- epilogue: O / l -> global; the two owners of a row add their sums ----
+    if (!timed_out && !mbar_wait(&bars.ofull, 0)) timed_out = true;
+    if (!timed_out) {
+      tc_fence_after();
+      fin_s[half * 128 + row] = l;
+      mbar_arrive(&bars.fin);
+      if (mbar_wait(&bars.fin, 0)) {
+        l = fin_s[row] + fin_s[128 + row];
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const bool row_ok = row0 + row < p.sq;
+        if (p.lse && row_ok && half == 0)  // one of the row's two owners; m is in the exp2 domain
+          p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + row] = l > 0.f ? (m_run + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        T* orow = ob + (int64_t)(row0 + (row_ok ? row : 0)) * p.o_ss + half * 64;
+#pragma unroll 1
+        for (int qd = 0; qd < 2; ++qd) {
+          uint32_t o[32];
+          tmem_ld32(t_o + lane_base + half * 64 + qd * 32, o);
+          tmem_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 w;
+              w.x = Elem<DT>::pack(__uint_as_float(o[c * 8 + 0]) * inv, __uint_as_float(o[c * 8 + 1]) * inv);
+              w.y = Elem<DT>::pack(__uint_as_float(o[c * 8 + 2]) * inv, __uint_as_float(o[c * 8 + 3]) * inv);
+              w.z = Elem<DT>::pack(__uint_as_float(o[c * 8 + 4]) * inv, __uint_as_float(o[c * 8 + 5]) * inv);
+              w.w = Elem<DT>::pack(__uint_as_float(o[c * 8 + 6]) * inv, __uint_as_float(o[c * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + qd * 32 + c * 8) = w;
+            }
+          }
+        }
+      } else {
+        timed_out = true;
+      }
+    }
+  }
+  if (timed_out && p.status) atomicOr(p.status, VA_STATUS_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 16) tmem_dealloc(tmem, 512);
+}
+
+template <int DT>
+int launch(const AttnParams& p, int batch, cudaStream_t stream) {
+  // per-device attribute; setting it on every launch keeps multi-device processes correct
+  if (cudaFuncSetAttribute(sparse_attn128_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess)
+    return VA_ERR_CUDA;
+  dim3 grid(p.nq, p.heads, batch);
+  sparse_attn128_kernel<DT><<<grid, kThreads, kSmem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
+}
+
+}  // namespace
+
+int launch_attn128(const AttnParams& p, int dtype, int batch, cudaStream_t stream) {
+  return dtype == VA_BF16 ? launch<VA_BF16>(p, batch, stream) : launch<VA_FP16>(p, batch, stream);
+}
+
+}  // namespace va
