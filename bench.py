@@ -386,6 +386,27 @@ def _reference_triton_select_ms(wl, thr):
         return None, f"reference Triton selection did not run: {type(e).__name__}: {e}"[:200]
 
 
+def _pre_attention_leg(wl, peaks):
+    """RMSNorm + rotary embedding of Q and K in one pass, on tensors of this workload's shape in (B,S,H*D) storage:
+    an HBM-bound kernel (every element read once, written once)."""
+    from vecattention_b200.preattn import qk_norm_rope
+    dev = wl.q.device
+    g = torch.Generator(device=dev).manual_seed(11)
+    q = torch.randn(wl.batch, wl.seq_len, wl.heads * D, generator=g, device=dev, dtype=torch.float32).to(wl.dtype)
+    k = torch.randn(wl.batch, wl.seq_len, wl.kv_heads * D, generator=g, device=dev, dtype=torch.float32).to(wl.dtype)
+    wq = torch.ones(wl.heads * D, dtype=wl.dtype, device=dev)
+    wk = torch.ones(wl.kv_heads * D, dtype=wl.dtype, device=dev)
+    ang = torch.rand(wl.seq_len, D // 2, generator=g, device=dev) * 6.283
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    qo, ko = torch.empty_like(q), torch.empty_like(k)
+    f = lambda: qk_norm_rope(q, k, wq, wk, 1e-6, cos, sin, heads=wl.heads, kv_heads=wl.kv_heads)
+    ms = time_cuda(f, 2, 5)
+    nbytes = 2 * (q.numel() + k.numel()) * 2 + 2 * cos.numel() * 4
+    del qo, ko
+    return {"kernel": "qk_norm_rope_kernel", "ms": ms, "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
+            "peak": peaks["hbm_gbs"], "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+
+
 def _measure(va, api, wl, thr, args, barrier, status, out):
     """Warm-up, then exactly ``args.steps`` timed steps bracketed by barrier + synchronize.  Returns ms for all steps."""
     pq, bk, g, chunk = wl.q_pooling_size, wl.k_local_size, wl.group_k_block, wl.chunk_size
@@ -559,6 +580,7 @@ def graft_arm(args):
     roofline, roofline_select = _rooflines(wl, peaks, stage, flops, counts)
     dense_ms, dense_which, dense_tried = _dense_baseline(wl)
     ref_sel_ms, ref_sel_note = _reference_triton_select_ms(wl, thr)
+    line["pre_attention"] = _pre_attention_leg(wl, peaks)
     line.update({"stage_ms": stage, "roofline": roofline, "roofline_select": roofline_select,
                  "dense_attention_ms": dense_ms,
                  "dense_attention": {"ms_this_gpus_heads": dense_ms, "kernel": dense_which, "tried_ms": dense_tried,

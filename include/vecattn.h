@@ -231,6 +231,37 @@ int va_prefill_static_fits(const va_prefill_args* args);
  * has VA_STATUS_TIMEOUT OR-ed in.  polls must be in [1, 4096]. */
 int va_selftest_wait_timeout(int32_t* status, int32_t polls, va_stream_t stream);
 
+/* ---- RMSNorm + rotary embedding of Q and K, feeding the operator without a layout change -----------
+ * Replaces, for a video-DiT attention layer (eval/DiTEvalKit/models/wan/attention.py:108-136), the RMSNorm
+ * of the projected Q and K over the hidden dimension (Triton kernel eval/DiTEvalKit/kernels/triton/
+ * rmsnorm.py:8-47), the three transposed copies to (B,H,S,D) (:123-128) and the in-place rotary embedding on
+ * interleaved element pairs (apply_qk_rope_inplace_cossin_complex, eval/DiTEvalKit/kernels/csrc/ops.h and
+ * include/rope/rope_enc_complex.cuh) by one pass over Q and K: the outputs keep the (B,S,H*D) storage, which
+ * va_prefill and the other entry points read in place as (B,H,S,D) with strides (H*D*S, D, H*D).
+ *   q, k        (B, S, heads*128) / (B, S, kv_heads*128), unit inner stride, row strides in elements
+ *   q_out, k_out  same shapes; may be the inputs themselves (in place)
+ *   q_weight, k_weight  RMSNorm weights of the hidden size in the tensors' dtype; NULL skips the norm
+ *   eps         added to the mean square
+ *   cos, sin    (S - rope_skip, 64) float32 tables, or NULL for no rotation; token s >= rope_skip uses row
+ *               s - rope_skip, earlier tokens are not rotated
+ * y = round16(x * rsqrt(mean(x^2) + eps) * w) in fp32, then per pair (y0, y1) -> round16(y0 cos - y1 sin),
+ * round16(y1 cos + y0 sin) in double precision, the reference kernels' arithmetic. */
+typedef struct {
+  int32_t dtype, batch, seq_len, heads, kv_heads, rope_skip;
+  const void* q;
+  const void* k;
+  int64_t q_row_stride, k_row_stride;
+  void* q_out;
+  void* k_out;
+  int64_t q_out_row_stride, k_out_row_stride;
+  const void* q_weight;
+  const void* k_weight;
+  float eps;
+  const float* cos;
+  const float* sin;
+} va_norm_rope_args;
+int va_qk_norm_rope(const va_norm_rope_args* args, va_stream_t stream);
+
 const char* va_status_string(int code);
 int va_version(void);
 

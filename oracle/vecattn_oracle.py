@@ -424,3 +424,42 @@ def seg_pr_per_head(q, k, block_size_q, block_size_k=16, group_size_k=16, thresh
                 recalls[bb, hh, i:i + n] = (probs[bb, hh] * mask).sum(-1)
                 sparsity[hh] += (1.0 - (mask.sum(-1).double() / see.sum(-1).double())).mean() * n
     return recalls.sum(dim=(0, 2)) / (b_ * s), sparsity / b_ / s
+
+
+# --------------------------------------------------------------------------------------
+# Q/K preparation of a video-DiT attention layer (RMSNorm over the hidden size, rotary embedding)
+# --------------------------------------------------------------------------------------
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm of the last dimension as the reference's Triton kernel computes it
+    (eval/DiTEvalKit/kernels/triton/rmsnorm.py:30-47): fp32 throughout, ``x * rstd`` then ``* w``, rounded to
+    the input dtype at the end.  (The association of the sum of squares is not specified there.)"""
+    xf = x.float()
+    rstd = 1.0 / torch.sqrt((xf * xf).sum(-1, keepdim=True) / x.shape[-1] + eps)
+    return ((xf * rstd) * weight.float()).to(x.dtype)
+
+
+def _round_from_double(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """float64 -> 16-bit type with ONE rounding to nearest, as the CUDA conversion the reference kernel uses
+    does.  (torch converts by way of float32, i.e. rounds twice; here the float32 step rounds to odd, after
+    which the final rounding to nearest is exact.)"""
+    f = x.to(torch.float32)
+    err = x - f.double()
+    bits = f.view(torch.int32)
+    inexact_even = (err != 0) & ((bits & 1) == 0) & torch.isfinite(f)
+    toward_larger_magnitude = (err > 0) == (f > 0)
+    bits = torch.where(inexact_even, torch.where(toward_larger_magnitude, bits + 1, bits - 1), bits)
+    return bits.view(torch.float32).to(dtype)
+
+
+def rope_interleaved(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, skip: int = 0) -> torch.Tensor:
+    """Rotary embedding on interleaved (even, odd) element pairs of (B, H, S, D), in double precision, rounded
+    to the input dtype: the in-place CUDA kernel of the reference (eval/DiTEvalKit/kernels/include/rope/
+    rope_enc_complex.cuh:27-45, tokens before ``skip`` untouched, :82-100), equivalently its PyTorch fallback
+    ``view_as_complex(x) * freqs`` (eval/DiTEvalKit/models/wan/attention.py:61-69).  ``cos`` / ``sin``: (S - skip, D/2)."""
+    out = x.clone()
+    xd = x[:, :, skip:].double()
+    e, o = xd[..., 0::2], xd[..., 1::2]
+    c, s = cos.double(), sin.double()
+    rot = torch.stack((e * c - o * s, o * c + e * s), dim=-1).flatten(-2)
+    out[:, :, skip:] = _round_from_double(rot, x.dtype)
+    return out

@@ -197,3 +197,23 @@ def test_reference_tuner_recall_and_sparsity(va, ref, causal):
           f"sparsity reference {ref_sparsity.float().tolist()} ours {sparsity.tolist()}")
     assert (recall - ref_recall.float()).abs().max() <= 6e-3
     assert (sparsity - ref_sparsity.float()).abs().max() <= 1.5e-2
+
+
+def test_reference_triton_rmsnorm(va, ref):
+    """The reference's Triton RMSNorm (eval/DiTEvalKit/kernels/triton/rmsnorm.py) against the fused kernel's
+    norm stage: equal except isolated results on the neighbouring 16-bit value (the sum of squares is
+    associated differently)."""
+    from eval.DiTEvalKit.kernels.triton.rmsnorm import triton_rmsnorm_forward
+    from vecattention_b200.preattn import qk_norm_rope
+    heads, s = 40, 777
+    x = _rand((1, s, heads * 128), 95, torch.bfloat16)
+    w = (1 + 0.1 * _rand((heads * 128,), 96, torch.float32)).to(torch.bfloat16)
+    theirs = triton_rmsnorm_forward(x, w, 1e-6)
+    theirs = theirs[0] if isinstance(theirs, tuple) else theirs
+    ours, _ = qk_norm_rope(x, x, w, w, 1e-6, heads=heads)
+    ours = ours.transpose(1, 2).reshape(1, s, heads * 128)
+    diff = ours != theirs
+    print(f"rmsnorm: {int(diff.sum())} of {ours.numel()} values differ from the reference Triton kernel")
+    assert diff.float().mean() <= 2e-3
+    step = theirs.float().abs().clamp_min(1e-3) * 2.0 ** -7
+    assert bool(((ours.float() - theirs.float()).abs() <= 1.01 * step).all())

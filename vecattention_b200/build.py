@@ -13,7 +13,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libvecattn.so")
-SOURCES = ["va_api.cu", "va_pool.cu", "va_select.cu", "va_attn.cu", "va_attn64.cu", "va_attn128.cu"]
+SOURCES = ["va_api.cu", "va_pool.cu", "va_select.cu", "va_attn.cu", "va_attn64.cu", "va_attn128.cu", "va_preattn.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -8,6 +8,7 @@ int pool_q(const va_pool_args& a, cudaStream_t stream);
 int select(const va_select_args& a, cudaStream_t stream);
 size_t select_workspace_bytes(int batch, int heads, int kv_heads, int nq, int sk);
 int sparse_attn(const va_attn_args& a, cudaStream_t stream);
+int qk_norm_rope(const va_norm_rope_args& a, cudaStream_t stream);
 
 // dense-block tables of query tiles [tile_off, tile_off + nqc) written as a contiguous (BH, nqc) slice
 __global__ void block_tables_kernel(int bh, int seq_len, int pq, int causal, int tile_off, int nqc,
@@ -161,6 +162,20 @@ int va_sparse_attn(const va_attn_args* a, va_stream_t stream) {
   if (int rc = check_tensor(a->v)) return rc;
   if (int rc = check_tensor(a->out)) return rc;
   return sparse_attn(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int va_qk_norm_rope(const va_norm_rope_args* a, va_stream_t stream) {
+  if (!a || !a->q || !a->k || !a->q_out || !a->k_out) return VA_ERR_NULL;
+  if ((a->cos == nullptr) != (a->sin == nullptr)) return VA_ERR_NULL;
+  if (a->dtype != VA_BF16 && a->dtype != VA_FP16) return VA_ERR_DTYPE;
+  if (a->batch <= 0 || a->seq_len <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->rope_skip < 0) return VA_ERR_SHAPE;
+  if (a->heads > 64 || a->kv_heads > 64) return VA_ERR_SHAPE;  // hidden sizes up to 8192
+  if ((int64_t)a->batch * a->seq_len > 0x7fffffff) return VA_ERR_SHAPE;
+  const void* ptrs[] = {a->q, a->k, a->q_out, a->k_out, a->q_weight, a->k_weight, a->cos, a->sin};
+  for (const void* p : ptrs)
+    if (p && !aligned16(p)) return VA_ERR_ALIGN;
+  if (a->q_row_stride % 8 || a->k_row_stride % 8 || a->q_out_row_stride % 8 || a->k_out_row_stride % 8) return VA_ERR_ALIGN;
+  return qk_norm_rope(*a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int va_block_tables(int32_t batch, int32_t heads, int32_t seq_len, int32_t pq, int32_t causal, int32_t* blk_count,
