@@ -476,7 +476,11 @@ def graft_arm(args):
     strong = args.scaling == "strong"
     if strong and world > cfg["kv_heads"]:
         raise SystemExit(f"{args.workload} has {cfg['kv_heads']} KV groups: it cannot be sharded over {world} GPUs")
-    if strong and world > 1:
+    if args.shard:  # one rank's share of the heads on a single GPU, without a process group (for kernel work)
+        r, n = (int(x) for x in args.shard.split("/"))
+        hs, _ = local_slices(cfg["heads"], cfg["kv_heads"], r, n)
+        wl = make_workload(args.workload, device=dev, heads=range(hs.start, hs.stop))
+    elif strong and world > 1:
         hs, _ = local_slices(cfg["heads"], cfg["kv_heads"], rank, world)
         wl = make_workload(args.workload, device=dev, heads=range(hs.start, hs.stop))
     else:
@@ -645,6 +649,7 @@ def main():
     ap.add_argument("--cpu-tiles", type=int, default=512, help="query tiles in the bounded CPU sample")
     ap.add_argument("--no-others", dest="others", action="store_false",
                     help="skip the brief measurement of the other configurations (one-GPU runs only)")
+    ap.add_argument("--shard", default="", help="r/n: run rank r's head shard of an n-way sharded layer on one GPU")
     ap.add_argument("--profile-window", action="store_true",
                     help="bracket the timed region with cudaProfilerStart/Stop (for `ncu --profile-from-start off`) "
                          "and skip the per-kernel, end-to-end and CPU legs")

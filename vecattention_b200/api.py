@@ -18,7 +18,22 @@ import torch
 
 from . import _lib as L
 
+import time
+
 SPATTN_BLOCK_SIZE_K = 64
+_FREE_MEMORY = {}  # device index -> (time of the query, free bytes): the query costs a fraction of a millisecond
+
+
+def _free_bytes(dev: torch.device) -> int:
+    """Free device memory, asked from the driver at most twice a second per device."""
+    now = time.monotonic()
+    hit = _FREE_MEMORY.get(dev.index)
+    if hit is None or now - hit[0] > 0.5:
+        hit = (now, torch.cuda.mem_get_info(dev)[0])
+        _FREE_MEMORY[dev.index] = hit
+    return hit[1]
+
+
 DEFAULT_COMPAT_BSQ = 64  # Triton program height of every causal launch config the reference ships
 
 
@@ -297,8 +312,7 @@ def VecAttention_prefill(
                          counts.data_ptr() if counts is not None else None,
                          status.data_ptr() if status is not None else None, 0)
     if single_pass_budget is None:
-        free, _ = torch.cuda.mem_get_info(dev)
-        single_pass_budget = max(1, min(32 << 30, int(free * 0.4)))
+        single_pass_budget = max(1, min(32 << 30, int(_free_bytes(dev) * 0.4)))
     args.single_pass_budget = int(single_pass_budget)
     nbytes = C.c_size_t(0)
     _check(L.lib().va_prefill_workspace_bytes(C.byref(args), C.byref(nbytes)))

@@ -49,6 +49,7 @@ struct SelectParams {
   int wpad;           // words per mask row (whole groups of four key tiles)
   int heads, kv_heads, rep, nq, sk;
   int pq, group_k_block;
+  int nseg;           // CTAs per block of 128 rows, each writing the keep bits of one segment of the key range
   int causal, wo_initial, compat_bsq, tile_offset, chunk_tiles;
 };
 
@@ -141,6 +142,7 @@ struct WalkShared {
 struct WalkArgs {
   uint32_t tmem;       // first accumulator buffer
   int t_lo, t_hi;      // key tiles the CTA walks
+  int t_keep;          // first tile whose keep bits this CTA writes (earlier tiles only feed the running maximum)
   int lo, k_hi;        // key range the CTA walks
   int sk, hi;          // sequence length; end of this thread's row
   int G;               // key blocks per group
@@ -261,6 +263,11 @@ __device__ __forceinline__ bool walk_rows(const WalkArgs& a, Barriers& bars, Wal
     }
     *rm_out = run;
     mbar_arrive(hand_out);
+    if (t < a.t_keep) {  // another CTA writes this tile's keep bits: only the running maximum was needed
+      tc_fence_before();
+      mbar_arrive(sempty);
+      continue;
+    }
     // ---- keep bits of the 128 keys ----
     uint32_t w[4];
 #pragma unroll
@@ -303,7 +310,8 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
   const int hkv = blockIdx.y, b = blockIdx.z;
   const int nrows = p.rep * p.nq;
   // causal rows walk more keys the later their tile: the longest walks are started first
-  const int row_base = (p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x) * kRows;
+  const int bx = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int row_base = (bx / p.nseg) * kRows, seg = bx % p.nseg;
 
   // ---- per-row limits: walker threads (warps 0-15) own row (warp % 4) * 32 + lane ----
   const bool is_walker = warp < kWalkerWarps;
@@ -325,8 +333,17 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
   __syncthreads();
   const int k_hi = s_khi;                       // CTA-wide end of the key walk
   const int t_lo = lo / kTile;
-  const int t_hi = (k_hi + kTile - 1) / kTile;  // exclusive
-  if (t_lo >= t_hi || k_hi <= lo) return;       // nothing selectable for any row of this CTA (the expansion writes zero counts)
+  int t_hi = (k_hi + kTile - 1) / kTile;  // exclusive
+  if (t_lo >= t_hi || k_hi <= lo) return;  // nothing selectable for any row of this CTA (the expansion writes zero counts)
+  // With few row blocks the key range is cut into segments, one CTA each: a CTA walks from the first tile (the
+  // running maximum is a prefix quantity) but forms keep bits only for its own segment, and stops after it.
+  int t_keep = t_lo;
+  if (p.nseg > 1) {
+    const int per = (t_hi - t_lo + p.nseg - 1) / p.nseg;
+    t_keep = t_lo + seg * per;
+    if (t_keep >= t_hi) return;
+    t_hi = min(t_hi, t_keep + per);
+  }
 
   unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
   unsigned char* q_s = smem;
@@ -421,6 +438,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
     a.tmem = tmem;
     a.t_lo = t_lo;
     a.t_hi = t_hi;
+    a.t_keep = t_keep;
     a.lo = lo;
     a.k_hi = k_hi;
     a.sk = p.sk;
@@ -502,7 +520,7 @@ int launch_bk(const SelectParams& p, const CUtensorMap& kmap, int batch, cudaStr
   auto kern = aligned ? select_mask_kernel<DT, BK, true> : select_mask_kernel<DT, BK, false>;
   // per-device attribute; setting it on every launch keeps multi-device processes correct
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess) return VA_ERR_CUDA;
-  dim3 grid(p.rows_pad / kRows, p.kv_heads, batch);
+  dim3 grid(p.rows_pad / kRows * p.nseg, p.kv_heads, batch);
   kern<<<grid, kThreads, kSmem, stream>>>(kmap, p);
   if (cudaGetLastError() != cudaSuccess) return VA_ERR_CUDA;
   const int64_t total_rows = (int64_t)batch * p.heads * p.nq;
@@ -560,6 +578,16 @@ int select(const va_select_args& a, cudaStream_t stream) {
   p.tile_offset = a.tile_offset;
   p.chunk_tiles = a.chunk_tiles;
   mask_geometry(a.heads, a.kv_heads, a.nq, a.sk, p.rows_pad, p.wpad);
+  {  // few CTAs: cut the key range so that more SMs take part (each extra segment re-walks the earlier ones' maxima)
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t ctas = (int64_t)(p.rows_pad / kRows) * a.kv_heads * a.batch;
+    const int tiles = (a.sk + kTile - 1) / kTile;
+    int nseg = (int)(sms / (ctas > 0 ? ctas : 1));
+    nseg = nseg < 1 ? 1 : (nseg > 4 ? 4 : nseg);
+    if (tiles < 64 * nseg) nseg = 1;  // short walks gain nothing
+    p.nseg = nseg;
+  }
   if (!a.workspace) return VA_ERR_NULL;
   if (a.workspace_bytes < select_workspace_bytes(a.batch, a.heads, a.kv_heads, a.nq, a.sk)) return VA_ERR_CAPACITY;
   if ((reinterpret_cast<uintptr_t>(a.workspace) & 15u) != 0) return VA_ERR_ALIGN;
