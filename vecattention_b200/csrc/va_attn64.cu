@@ -19,7 +19,7 @@
 //   warps 8-11  K gather producers, warps 12-15 V gather producers: cp.async 16-byte pieces of the
 //              selected rows into rings of 128-byte-swizzled operand tiles (2 K stages, 3 V
 //              stages); copy completion is reported to the stage's mbarrier asynchronously; index
-//              loads run two chunks ahead and are exchanged inside the warp with shuffles.
+//              loads run two chunks ahead and are exchanged inside the warp through shared memory.
 //   warps 16,17  MMA issuers (one thread each): warp 16 issues S_j = Q K_j^T, warp 17 issues
 //              O += P_j V_j; S and P are double buffered, so the tensor pipe works on S_{j+1} and
 //              O += P_{j-1} V_{j-1} while softmax j runs.
@@ -45,6 +45,9 @@ constexpr int kThreads = 576;
 // producer warpgroups hand 40 each back and the two softmax warpgroups take them:
 // 256 * 56 + 256 * 136 + 64 * 96 = 576 * 96.
 constexpr int kProducerRegs = 56, kSoftmaxRegs = 136;
+// The softmax warps can only take what the producer warps hand back (the CTA's own allocation is the pool); if the
+// sum exceeded the launch allocation they would wait for registers nobody releases.
+static_assert(256 * kProducerRegs + 256 * kSoftmaxRegs + 64 * 96 <= kThreads * 96, "setmaxnreg pool");
 constexpr size_t kSmem = 1024 + (size_t)kQTile * 3 + (size_t)kKvTile * (kKStages + kVStages);  // Q, P x2, K ring, V ring
 constexpr float kRescaleThreshold = 8.0f;                                            // log2 units
 
@@ -77,6 +80,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int keys_s[8][kChunk];  // ring deep enough that a slot is rewritten long after its last reader
+  __shared__ __align__(16) int xk_s[8][2][32];  // per producer warp: the lanes' key indices of a chunk, for the exchange
   __shared__ __align__(16) int mask_s[8][4];  // per chunk and K producer warp: does any of its keys need masking?
   __shared__ float xch_s[2][256];   // [group][phase][TMEM lane]: chunk maxima swapped by a row's two owners
   __shared__ float m_row_s[2][64];   // [chunk parity][row]: the rows' shared reference maxima (exp2 domain)
@@ -110,13 +114,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   unsigned char* v_s = k_s + (size_t)kKStages * kKvTile;           // V ring
 
   if (tid == 0) {
-    mbar_init(&bars.qfull, 256);  // per producer thread: one asynchronous copy-completion arrival + one plain arrival
+    mbar_init(&bars.qfull, 128);  // per producer thread: one arrival, made by the hardware when the thread's copies have landed
     for (int s = 0; s < kKStages; ++s) {
-      mbar_init(&bars.kfull[s], 256);
+      mbar_init(&bars.kfull[s], 128);
       mbar_init(&bars.kempty[s], 1);
     }
     for (int s = 0; s < kVStages; ++s) {
-      mbar_init(&bars.vfull[s], 256);
+      mbar_init(&bars.vfull[s], 128);
       mbar_init(&bars.vempty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -161,14 +165,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
         cp_async16(smem_addr(q_s + tile_off(64, r, c)), qb + (int64_t)(ok ? row0 + r : 0) * p.q_ss + c * 8, ok);
       }
       cp_async_arrive_noinc(&bars.qfull);
-      mbar_arrive(&bars.qfull);
     }
     // Copy geometry.  A warp covers two key rows per instruction: lanes 0-15 the sixteen 16-byte
     // pieces of row rbase + 8 i, lanes 16-31 those of the next row.  Because the rows of one thread
     // differ by multiples of 8, its swizzled piece position is the same in all of them and the
     // shared-memory destinations are one base address plus i * 1024.
     // Each lane fetches ONE key index per chunk (that of row rbase + 8 * (lane & 15)), one chunk
-    // ahead; the sixteen indices a thread needs are then exchanged with warp shuffles.
+    // ahead; the sixteen indices a thread needs are then exchanged through shared memory.
     const int pw = (pt >> 5), hi = lane >> 4, c = lane & 15;
     const int rbase = 2 * pw + hi;
     const uint32_t dst_off = tile_off(128, rbase, c);
@@ -185,11 +188,20 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       const int key = slot < nblk * 64 ? raw + (slot & 63) : (slot < nslots ? raw : -1);
       return (key >= 0 && key < p.sk) ? key : -1;
     };
-    // all sixteen keys of this thread's rows, from the lanes that fetched them
-    auto spread = [&](int key, int (&out)[16]) {
-      const int kcl = max(key, 0);  // an unused slot copies row 0: its scores are masked and its P is zero
+    // All sixteen keys of this thread's rows, from the lanes that fetched them: through a small exchange array of
+    // the warp (one store and four 16-byte loads per thread instead of sixteen shuffles; two buffers, so the
+    // next chunk's stores cannot overtake this chunk's loads).
+    int* xk = xk_s[warp - 8][0];
+    auto spread = [&](int j, int key, int (&out)[16]) {
+      int* buf = xk + (j & 1) * 32;
+      buf[lane] = max(key, 0);  // an unused slot copies row 0: its scores are masked and its P is zero
+      __syncwarp();
+      const int4* src = reinterpret_cast<const int4*>(buf + (lane & 16));
 #pragma unroll
-      for (int i = 0; i < 16; ++i) out[i] = __shfl_sync(0xffffffffu, kcl, (lane & 16) + i);
+      for (int i = 0; i < 4; ++i) {
+        const int4 q4 = src[i];
+        out[4 * i] = q4.x; out[4 * i + 1] = q4.y; out[4 * i + 2] = q4.z; out[4 * i + 3] = q4.w;
+      }
     };
     auto copy_tile = [&](unsigned char* tile, const T* base, int64_t stride, const int (&keys)[16], uint64_t* full) {
       const uint32_t dst = smem_addr(tile) + dst_off;
@@ -197,7 +209,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
 #pragma unroll
       for (int i = 0; i < 16; ++i) cp_async16_full(dst + i * 1024, src + (int64_t)keys[i] * stride);
       cp_async_arrive_noinc(full);
-      mbar_arrive(full);
     };
     // K and V have producer warps of their own, so neither copy waits behind the other's stage:
     // a K stage is free as soon as S has been computed from it, a V stage only after the PV
@@ -217,7 +228,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
           const int any = __any_sync(0xffffffffu, flag);
           if (lane == 0) mask_s[j & 7][pw] = any;
         }
-        spread(key, keys);
+        spread(j, key, keys);
         if (!is_v) {
           const int ks = j % kKStages, ku = j / kKStages;
           if (!mbar_wait(&bars.kempty[ks], (ku & 1) ^ 1)) { timed_out = true; break; }
