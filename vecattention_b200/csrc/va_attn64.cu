@@ -55,6 +55,23 @@ struct Barriers {
   uint64_t qfull, kfull[kKStages], kempty[kKStages], vfull[kVStages], vempty[kVStages];
   uint64_t sfull[2], sempty[2], pfull[2], pempty[2], ofull, xch[4], dec[2], fin;
 };
+// Expected arrivals, in the order of the members above (thread i initialises barrier i).  The "full" barriers of
+// the gathered tiles count one arrival per producer thread, made by the hardware when the thread's copies have landed.
+constexpr int kNumBarriers = sizeof(Barriers) / sizeof(uint64_t);
+__device__ __forceinline__ uint32_t barrier_count(int i) {
+  constexpr int kq = 0, kf = kq + 1, ke = kf + kKStages, vf = ke + kKStages, ve = vf + kVStages, sf = ve + kVStages;
+  constexpr int se = sf + 2, pf = se + 2, pe = pf + 2, of = pe + 2, xc = of + 1, dc = xc + 4, fn = dc + 2;
+  static_assert(fn + 1 == kNumBarriers, "barrier table out of step with struct Barriers");
+  if (i < ke) return 128;              // qfull, kfull
+  if (i < vf) return 1;                // kempty
+  if (i < ve) return 128;              // vfull
+  if (i < se) return 1;                // vempty, sfull
+  if (i < pe) return 128;              // sempty, pfull
+  if (i < xc) return 1;                // pempty, ofull
+  if (i < dc) return 64;               // xch
+  if (i < fn) return 128;              // dec
+  return 256;                          // fin
+}
 
 // Register hand-over between warpgroups (four consecutive warps, all of which execute it).
 template <int N>
@@ -113,26 +130,22 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   unsigned char* k_s = smem + 3 * kQTile;                          // K ring
   unsigned char* v_s = k_s + (size_t)kKStages * kKvTile;           // V ring
 
-  if (tid == 0) {
-    mbar_init(&bars.qfull, 128);  // per producer thread: one arrival, made by the hardware when the thread's copies have landed
-    for (int s = 0; s < kKStages; ++s) {
-      mbar_init(&bars.kfull[s], 128);
-      mbar_init(&bars.kempty[s], 1);
-    }
-    for (int s = 0; s < kVStages; ++s) {
-      mbar_init(&bars.vfull[s], 128);
-      mbar_init(&bars.vempty[s], 1);
-    }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars.sfull[s], 1);
-      mbar_init(&bars.sempty[s], 128);
-      mbar_init(&bars.pfull[s], 128);
-      mbar_init(&bars.pempty[s], 1);
-      mbar_init(&bars.dec[s], 128);
-    }
-    for (int s = 0; s < 4; ++s) mbar_init(&bars.xch[s], 64);
-    mbar_init(&bars.fin, 256);
-    mbar_init(&bars.ofull, 1);
+  // The producers' first two index loads start before the set-up, so that their latency overlaps it.
+  const int32_t* blk = p.blk_idx + trow * p.blk_stride;
+  const int32_t* col = p.col_idx + trow * p.col_stride;
+  auto fetch_raw = [&](int j, int my_slot) -> int {
+    const int slot = j * kChunk + my_slot;
+    const int ci = min(max(slot - nblk * 64, 0), max(ncol - 1, 0));
+    return ldg_nc(slot < nblk * 64 ? blk + (slot >> 6) : col + ci);
+  };
+  int raw_first = 0, raw_second = 0;
+  if (warp >= 8 && warp < 16) {
+    const int my_slot = 2 * (warp & 3) + (lane >> 4) + 8 * (lane & 15);
+    raw_first = fetch_raw(0, my_slot);
+    raw_second = nchunks > 1 ? fetch_raw(1, my_slot) : 0;
+  }
+  if (tid < kNumBarriers) {
+    mbar_init(reinterpret_cast<uint64_t*>(&bars) + tid, barrier_count(tid));
     fence_proxy_async();
   }
   if (warp == 16) {
@@ -155,8 +168,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     const T* qb = static_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
     const T* kb = static_cast<const T*>(p.k) + b * p.k_sb + hkv * p.k_sh;
     const T* vb = static_cast<const T*>(p.v) + b * p.v_sb + hkv * p.v_sh;
-    const int32_t* blk = p.blk_idx + trow * p.blk_stride;
-    const int32_t* col = p.col_idx + trow * p.col_stride;
     if (!is_v) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {  // Q tile: rows beyond the sequence are zero
@@ -176,13 +187,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     const int rbase = 2 * pw + hi;
     const uint32_t dst_off = tile_off(128, rbase, c);
     const int my_slot = rbase + 8 * c;
-    // The raw load is issued one chunk ahead and only interpreted at the top of the next iteration,
-    // so the (in-order) warp never stalls on the index fetch.
-    auto fetch_raw = [&](int j) -> int {
-      const int slot = j * kChunk + my_slot;
-      const int ci = min(max(slot - nblk * 64, 0), max(ncol - 1, 0));
-      return ldg_nc(slot < nblk * 64 ? blk + (slot >> 6) : col + ci);
-    };
     auto decode = [&](int j, int raw) -> int {
       const int slot = j * kChunk + my_slot;
       const int key = slot < nblk * 64 ? raw + (slot & 63) : (slot < nslots ? raw : -1);
@@ -216,11 +220,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     // later iteration, so the in-order warp never stalls on them.
     {
       int keys[16];
-      int raw0 = fetch_raw(0), raw1 = nchunks > 1 ? fetch_raw(1) : 0;
+      int raw0 = raw_first, raw1 = raw_second;
       for (int j = 0; j < nchunks && !timed_out; ++j) {
         const int key = decode(j, raw0);
         raw0 = raw1;
-        if (j + 2 < nchunks) raw1 = fetch_raw(j + 2);
+        if (j + 2 < nchunks) raw1 = fetch_raw(j + 2, my_slot);
         if (!is_v) {
           keys_s[j & 7][my_slot] = key;
           // unused slots, and keys that some row of the tile may not see, make the chunk take the masking pass
