@@ -37,10 +37,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu
 # capture summarised under profiles/ (workload -> bytes); None until a capture exists
 # workload -> bytes; c4 was captured at full size (one-pass metrics): profiles/launch_list_c4.md
-NCU_TRAFFIC_BYTES = {"c2h8": 303.9e6, "c4": 6.24e9 + 0.726e9}  # profiles/sparse_attn64_kernel_c2h8.md
-NCU_SELECT_TRAFFIC_BYTES = {"c4": (729.9e6 + 12.9e6) + (810.9e6 + 649.6e6) + (670.3e6 + 1.71e9)}  # pool + mask + expand
+NCU_TRAFFIC_BYTES = {"c2h8": 303.4e6, "c4": 6.30e9 + 0.725e9}  # profiles/sparse_attn64_kernel_c2h8.md
+NCU_SELECT_TRAFFIC_BYTES = {"c4": (729.9e6 + 12.9e6) + (810.9e6 + 658.3e6) + (670.5e6 + 1.71e9)}  # pool + mask + expand
 # the capture is of 8 heads; DRAM traffic of this kernel grows in proportion to the heads processed
-NCU_TRAFFIC_PER_HEAD_32K = 303.9e6 / 8
+NCU_TRAFFIC_PER_HEAD_32K = 303.4e6 / 8
 D = 128
 CONFIG_HEADS = {"c2": 32, "c3": 40, "c4": 24, "c5": 28, "c2h8": 8}
 
