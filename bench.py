@@ -304,7 +304,7 @@ def _rooflines(wl, peaks, stage, flops, counts):
     full = wl.heads == CONFIG_HEADS.get(wl.name)
     traffic = (NCU_TRAFFIC_PER_HEAD_32K * wl.heads if wl.name in ("c2", "c2h8") else
                NCU_TRAFFIC_BYTES.get(wl.name) if full else None)
-    roofline = {"kernel": "sparse_attn64_kernel" if wl.q_pooling_size == 64 else "sparse_attn_kernel", "bound": "tensor",
+    roofline = {"kernel": "sparse_attn64_kernel" if wl.q_pooling_size == 64 else "sparse_attn128_kernel", "bound": "tensor",
                 "achieved": achieved_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved_tf / peaks["bf16_tflops"], "traffic": traffic,
                 "traffic_note": ("ncu capture of 8 heads x 32 K tokens, scaled by heads" if wl.name in ("c2", "c2h8") else
