@@ -109,6 +109,34 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   const int hkv = h / p.rep;
   const int row0 = tile * PQ;
   const int64_t trow = ((int64_t)b * p.heads + h) * p.nq + tile;
+
+  unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+  unsigned char* q_s = smem;
+  unsigned char* p_s = smem + kQTile;       // two buffers
+  unsigned char* k_s = smem + 3 * kQTile;                          // K ring
+  unsigned char* v_s = k_s + (size_t)kKStages * kKvTile;           // V ring
+
+  // The start of a tile is a chain of memory latencies (counts -> indices -> rows -> first product).  What only
+  // depends on the tile's position is requested before the counts are known: the Q tile, and the first two chunks'
+  // column indices (speculatively: a tile with dense blocks, which come first in slot order, fetches again).
+  const int32_t* blk = p.blk_idx + trow * p.blk_stride;
+  const int32_t* col = p.col_idx + trow * p.col_stride;
+  int raw_first = 0, raw_second = 0;
+  if (warp >= 8 && warp < 16) {
+    if (warp < 12) {
+      const int pt = tid - 256;
+      const T* qb = static_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {  // Q tile: rows beyond the sequence are zero
+        const int pce = pt + i * 128, r = pce >> 4, c = pce & 15;
+        const bool ok = row0 + r < p.sq;
+        cp_async16(smem_addr(q_s + tile_off(64, r, c)), qb + (int64_t)(ok ? row0 + r : 0) * p.q_ss + c * 8, ok);
+      }
+    }
+    const int my_slot = 2 * (warp & 3) + (lane >> 4) + 8 * (lane & 15);
+    if (my_slot < p.col_stride) raw_first = ldg_nc(col + my_slot);
+    if (kChunk + my_slot < p.col_stride) raw_second = ldg_nc(col + kChunk + my_slot);
+  }
   const int nblk = p.blk_count ? __ldg(p.blk_count + trow) : 0;
   const int ncol = __ldg(p.col_count + trow);
   const int nslots = nblk * 64 + ncol;
@@ -121,25 +149,17 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       if (row0 + r < p.sq) *reinterpret_cast<uint4*>(ob + (int64_t)(row0 + r) * p.o_ss + c * 8) = make_uint4(0, 0, 0, 0);
     }
     if (p.lse && tid < PQ && row0 + tid < p.sq) p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + tid] = -INFINITY;
+    cp_async_commit();
+    cp_async_wait<0>();  // the Q copies requested above must not outlive the CTA
     return;
   }
 
-  unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
-  unsigned char* q_s = smem;
-  unsigned char* p_s = smem + kQTile;       // two buffers
-  unsigned char* k_s = smem + 3 * kQTile;                          // K ring
-  unsigned char* v_s = k_s + (size_t)kKStages * kKvTile;           // V ring
-
-  // The producers' first two index loads start before the set-up, so that their latency overlaps it.
-  const int32_t* blk = p.blk_idx + trow * p.blk_stride;
-  const int32_t* col = p.col_idx + trow * p.col_stride;
   auto fetch_raw = [&](int j, int my_slot) -> int {
     const int slot = j * kChunk + my_slot;
     const int ci = min(max(slot - nblk * 64, 0), max(ncol - 1, 0));
     return ldg_nc(slot < nblk * 64 ? blk + (slot >> 6) : col + ci);
   };
-  int raw_first = 0, raw_second = 0;
-  if (warp >= 8 && warp < 16) {
+  if (nblk > 0 && warp >= 8 && warp < 16) {
     const int my_slot = 2 * (warp & 3) + (lane >> 4) + 8 * (lane & 15);
     raw_first = fetch_raw(0, my_slot);
     raw_second = nchunks > 1 ? fetch_raw(1, my_slot) : 0;
@@ -165,18 +185,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     reg_dealloc<kProducerRegs>();
     const bool is_v = warp >= 12;
     const int pt = is_v ? tid - 384 : tid - 256;
-    const T* qb = static_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
     const T* kb = static_cast<const T*>(p.k) + b * p.k_sb + hkv * p.k_sh;
     const T* vb = static_cast<const T*>(p.v) + b * p.v_sb + hkv * p.v_sh;
-    if (!is_v) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {  // Q tile: rows beyond the sequence are zero
-        const int pce = pt + i * 128, r = pce >> 4, c = pce & 15;
-        const bool ok = row0 + r < p.sq;
-        cp_async16(smem_addr(q_s + tile_off(64, r, c)), qb + (int64_t)(ok ? row0 + r : 0) * p.q_ss + c * 8, ok);
-      }
-      cp_async_arrive_noinc(&bars.qfull);
-    }
+    if (!is_v) cp_async_arrive_noinc(&bars.qfull);  // the Q copies were issued at the top of the kernel
     // Copy geometry.  A warp covers two key rows per instruction: lanes 0-15 the sixteen 16-byte
     // pieces of row rbase + 8 i, lanes 16-31 those of the next row.  Because the rows of one thread
     // differ by multiples of 8, its swizzled piece position is the same in all of them and the
