@@ -9,13 +9,17 @@
 //    consecutive rows of that list and walks the keys of its KV head once, 128 keys per tile, in
 //    ascending order, so the running (prefix) maximum of a key-block group is a per-thread register.
 //    Warp roles (608 threads, one CTA per SM):
-//      warps 0-15  row walkers: pooled row r = TMEM lane r is owned by four threads, one per 32-key
-//                 quarter of the tile (warp w walks quarter w / 4 of the rows of lane quarter w % 4,
-//                 the only lanes it can reach).  Per tile each pulls its 32 estimates into registers
-//                 and forms the maxima of its key blocks; the four swap them through shared memory
-//                 (one meeting per tile), so all know the running maximum entering every block;
-//                 each builds the 32-bit keep mask fp32(s + gap) >= m of its quarter.  The words
-//                 are collected in shared memory and leave as 64-byte row pieces every four tiles.
+//      warps 0-15  row walkers, by turns: warp w can reach TMEM lane quarter w % 4 (32 pooled rows) and takes
+//                 every fourth key tile (tiles n with n % 4 == w / 4, accumulator buffer w / 4), so the four
+//                 warps of a scheduler work on four different tiles.  A thread walks its row's whole tile:
+//                 it reads the 128 estimates and forms the maxima of the tile's key blocks, receives the
+//                 row's running maximum after the previous tile from the warp that walked it (one float
+//                 per row through shared memory, an mbarrier per warp pair), forms the running maximum
+//                 entering every block and hands the one after its tile on at once; then it reads the
+//                 estimates again, builds the 128 keep bits fp32(s + gap) >= m and stores them as one
+//                 16-byte piece of the row's mask.  With few row blocks the key range is cut into up to
+//                 four segments (one CTA each): a CTA still walks from the first tile for the maxima but
+//                 writes keep bits only for its own segment.
 //      warp 16    one thread streams K: a TMA tensor-map copy per 128-key tile (two boxes of 128 rows
 //                 x 128 bytes, 128-byte swizzle) into a 4-stage ring; rows past the sequence read as zeros.
 //      warps 17,18 one thread each issues S_t = Q~ K_t^T for alternate tiles, 128 x 128 x 128 as eight
