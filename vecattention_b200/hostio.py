@@ -37,7 +37,7 @@ def VecAttention_prefill_host(
     *,
     out: Optional[torch.Tensor] = None,
     device: Union[str, torch.device, None] = None,
-    slices: int = 12,
+    slices: int = 24,
     compat_q1: bool = True,
     staging: Optional[dict] = None,
 ) -> torch.Tensor:
