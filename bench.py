@@ -507,12 +507,12 @@ def graft_arm(args):
     if args.shard:  # one rank's share of the heads on a single GPU, without a process group (for kernel work)
         r, n = (int(x) for x in args.shard.split("/"))
         hs, _ = local_slices(cfg["heads"], cfg["kv_heads"], r, n)
-        wl = make_workload(args.workload, device=dev, heads=range(hs.start, hs.stop))
+        wl = make_workload(args.workload, device=dev, heads=range(hs.start, hs.stop), keep=args.keep or None)
     elif strong and world > 1:
         hs, _ = local_slices(cfg["heads"], cfg["kv_heads"], rank, world)
-        wl = make_workload(args.workload, device=dev, heads=range(hs.start, hs.stop))
+        wl = make_workload(args.workload, device=dev, heads=range(hs.start, hs.stop), keep=args.keep or None)
     else:
-        wl = make_workload(args.workload, device=dev, sample_seed=rank)
+        wl = make_workload(args.workload, device=dev, sample_seed=rank, keep=args.keep or None)
     pq, bk, g, chunk = wl.q_pooling_size, wl.k_local_size, wl.group_k_block, wl.chunk_size
     thr = _calibrated_threshold(va, wl, args)
     if world > 1 and strong and not args.threshold:  # one threshold for the layer: rank 0's calibration
@@ -642,8 +642,10 @@ def graft_arm(args):
         others = {}
         del wl, out, counts, bcnt, bidx
         torch.cuda.empty_cache()
-        for name in [w for w in ("c2", "c3", "c4", "c5", "d128") if w != args.workload]:
-            owl = make_workload(name, device=dev)
+        # (configuration 3 also at half and twice its keep ratio)
+        todo = [(w, None) for w in ("c2", "c3", "c4", "c5", "d128") if w != args.workload] + [("c3", 0.05), ("c3", 0.20)]
+        for name, okeep in todo:
+            owl = make_workload(name, device=dev, keep=okeep)
             othr = _calibrated_threshold(va, owl, args)
             oout = torch.empty_like(owl.q)
             _, ocnt = va.VecAttention_prefill(owl.q, owl.k, owl.v, othr, owl.q_pooling_size, owl.k_local_size,
@@ -654,7 +656,7 @@ def graft_arm(args):
             oms = _measure(va, api, owl, othr, oargs, barrier, status, oout) / 3
             ostage = _stage_times(va, api, owl, othr, ocnt, obc, obi, oout)
             orf, ors = _rooflines(owl, peaks, ostage, oflops, ocnt)
-            others[name] = {"ms_per_layer": oms, "effective_tflops": oflops / (oms * 1e-3) / 1e12, "threshold": othr,
+            others[name if okeep is None else f"{name}_keep{int(round(okeep * 100)):02d}"] = {"ms_per_layer": oms, "effective_tflops": oflops / (oms * 1e-3) / 1e12, "threshold": othr,
                             "keep_ratio": float(ocnt.sum()) / (owl.eligible_pairs_per_head() * owl.heads * owl.batch),
                             "stage_ms": ostage, "roofline_frac": orf["frac"], "roofline_select_frac": ors["frac"]}
             del owl, oout, ocnt, obc, obi
@@ -674,6 +676,7 @@ def main():
     ap.add_argument("--workload", default="c4", choices=["c2", "c3", "c4", "c5", "d128", "c2h8", "mini"])
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--threshold", type=float, default=0.0, help="skip calibration and use this MinP threshold")
+    ap.add_argument("--keep", type=float, default=0.0, help="calibrate the threshold to this keep ratio instead of the workload's")
     ap.add_argument("--cpu-tiles", type=int, default=512, help="query tiles in the bounded CPU sample")
     ap.add_argument("--no-others", dest="others", action="store_false",
                     help="skip the brief measurement of the other configurations (one-GPU runs only)")
