@@ -76,3 +76,12 @@ def test_static_scratch_prefill_equals_workspace_prefill_twice(built_library):
         err = (out_st.float() - out_ws.float()).abs()
         assert torch.isfinite(out_st.float()).all()
         assert err.max() <= 2e-2 and err.mean() <= 2e-3, f"call {call}: {err.max().item()}"
+        if call < 2:  # and against the CPU oracle (the third problem would take it minutes)
+            import math
+            from oracle import vecattn_oracle as O
+            ref, sel = O.vecattention_prefill(q.cpu(), k.cpu(), v.cpu(), math.exp(-0.6931) - 1e-9, 64, 16, 16, causal, chunk,
+                                              return_selection=True)
+            ref_counts = torch.cat([c for c, _ in sel], dim=2)
+            assert (cnt_st.cpu() - ref_counts).abs().sum() <= 2, f"call {call}: counts differ from the oracle"
+            err = (out_st.float().cpu() - ref.float()).abs()
+            assert err.max() <= 2e-2 and err.mean() <= 2e-3, f"call {call} vs oracle: {err.max().item()}"
