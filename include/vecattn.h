@@ -122,7 +122,15 @@ int va_select_workspace_bytes(const va_select_args* args, size_t* bytes);
  *   softmax_scale 0 selects 1/sqrt(D).  A tile with no key at all writes zeros.
  *   lse        optional (B,H,Sq) float32 contiguous: natural-log sum of exp(score * scale) over the
  *              row's visible keys (the reference API's return_softmax_lse); -inf for a row without keys.
- *   Indices must satisfy 0 <= idx < Sk. */
+ *   Indices must satisfy 0 <= idx < Sk.
+ *
+ * Vision-slice composition in one launch (vision_mode = 1; pq 64, causal, Sq == Sk, q_offset 0).
+ * Replaces the three attention calls and the concatenation of the "vecattention" branch of
+ * customize_prefill_attention, spattn/src/models/utils.py:97-128: rows [0, vision_begin) get full causal
+ * attention, rows [vision_begin, vision_end) the sparse attention of their query tile, rows
+ * [vision_end, Sq) full causal attention over all keys.  The tables then describe the query tiles of
+ * rows [0, vision_end) only (nq = ceil(vision_end / 64) entries per head, as the selection over those rows
+ * produced them); the dense parts need no tables.  0 <= vision_begin <= vision_end <= Sq. */
 typedef struct {
   int32_t dtype, batch, heads, kv_heads, sq, sk, head_dim, pq;
   int32_t causal, q_offset;
@@ -137,6 +145,7 @@ typedef struct {
   float softmax_scale;
   int32_t* status; /* optional device word receiving VA_STATUS_* bits */
   float* lse;      /* optional, see above */
+  int32_t vision_mode, vision_begin, vision_end; /* see above; all zero: off */
 } va_attn_args;
 int va_sparse_attn(const va_attn_args* args, va_stream_t stream);
 /* Scratch va_sparse_attn needs besides its outputs: none (bytes = 0); the reference call site makes

@@ -297,10 +297,11 @@ def test_host_buffer_pipeline_equals_device_call(va, slices, pinned):
 
 
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("vs,ve", [(37, 1900), (None, 1500), (200, None), (0, 2048), (64, 64)])
+@pytest.mark.parametrize("vs,ve", [(37, 1900), (None, 1500), (200, None), (0, 2048), (64, 64), (130, 131), (1000, 1087)])
 def test_vision_slice_composition_matches_oracle(va, vs, ve):
     """Dense text prefix / VecAttention up to the end of the vision span / dense text suffix
-    (the reference dispatcher's composition), GQA, positions that are not tile multiples."""
+    (the reference dispatcher's composition), GQA, positions that are not tile multiples; the
+    one-launch form and the three-launch form give the same bits."""
     b, h, hkv, s = 1, 4, 2, 2048
     q = _rand((b, h, s, 128), 31, torch.bfloat16)
     k = _rand((b, hkv, s, 128), 32, torch.bfloat16)
@@ -309,6 +310,9 @@ def test_vision_slice_composition_matches_oracle(va, vs, ve):
     ref = O.vecattention_prefill_vision(q, k, v, 0.7, 64, 16, 16, 1024, vs, ve).float()
     got = va.VecAttention_prefill_vision(q.cuda(), k.cuda(), v.cuda(), 0.7, 64, 16, 16, True, 1024,
                                          vision_start_position=vs, vision_end_position=ve).float().cpu()
+    three = va.VecAttention_prefill_vision(q.cuda(), k.cuda(), v.cuda(), 0.7, 64, 16, 16, True, 1024,
+                                           vision_start_position=vs, vision_end_position=ve, fused=False).float().cpu()
+    assert torch.equal(got, three), "one launch and three launches must agree bit for bit"
     err = (got - ref).abs()
     assert torch.isfinite(got).all()
     assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS, (err.max().item(), err.mean().item())

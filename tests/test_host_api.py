@@ -36,7 +36,7 @@ def test_struct_layout_matches_header(lib):
     assert C.sizeof(lib.Tensor4) == 32
     assert C.sizeof(lib.PoolArgs) == 24 + 32 + 8
     assert C.sizeof(lib.SelectArgs) == 56 + 8 + 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8
-    assert C.sizeof(lib.AttnArgs) == 40 + 4 * 32 + 8 * 6 + 8 + 8 + 8
+    assert C.sizeof(lib.AttnArgs) == 40 + 4 * 32 + 8 * 6 + 8 + 8 + 8 + 16   # ... + three int32 and padding
     assert C.sizeof(lib.NormRopeArgs) == 24 + 8 * 8 + 8 * 2 + 8 + 8 + 8
     assert C.sizeof(lib.PrefillArgs) == 56 + 4 * 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8
 
@@ -72,6 +72,19 @@ def test_validation_returns_codes_without_launching(lib):
     s.bk, s.capacity = 16, 0
     assert h.va_select(C.byref(s), None) == -5          # capacity
     assert h.va_block_tables(1, 1, 128, 64, 1, None, None, None) == -1
+    # vision-slice composition: 64-row tiles, causal, one sequence for queries and keys, ordered positions
+    t = lib.Tensor4(256, 0, 0, 128)
+    at = lib.AttnArgs(0, 1, 2, 2, 512, 512, 128, 64, 1, 0, t, t, t, t, None, None, 0, 256, 256, 16, 0.0, None, None, 1, 100, 400)
+    at.pq = 128
+    assert h.va_sparse_attn(C.byref(at), None) == -7
+    at.pq, at.causal = 64, 0
+    assert h.va_sparse_attn(C.byref(at), None) == -7
+    at.causal, at.sk = 1, 1024
+    assert h.va_sparse_attn(C.byref(at), None) == -7
+    at.sk, at.vision_begin = 512, 401
+    assert h.va_sparse_attn(C.byref(at), None) == -3
+    at.vision_begin, at.vision_end = 100, 513
+    assert h.va_sparse_attn(C.byref(at), None) == -3
 
 
 def test_prefill_workspace_bytes(lib):

@@ -50,7 +50,8 @@ class AttnArgs(C.Structure):
                 ("q", Tensor4), ("k", Tensor4), ("v", Tensor4), ("out", Tensor4),
                 ("blk_count", C.c_void_p), ("blk_idx", C.c_void_p), ("blk_stride", C.c_int64),
                 ("col_count", C.c_void_p), ("col_idx", C.c_void_p), ("col_stride", C.c_int64),
-                ("softmax_scale", C.c_float), ("status", C.c_void_p), ("lse", C.c_void_p)]
+                ("softmax_scale", C.c_float), ("status", C.c_void_p), ("lse", C.c_void_p),
+                ("vision_mode", C.c_int32), ("vision_begin", C.c_int32), ("vision_end", C.c_int32)]
 
 
 class PrefillArgs(C.Structure):

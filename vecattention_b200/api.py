@@ -119,15 +119,17 @@ def fuse_qk_softmax_minp_wo_causal(avg_q_chunk: torch.Tensor, k: torch.Tensor, a
                                    q_pooling_size: int = 128, k_local_size: int = 128,
                                    wo_initial: bool = False, group_k_block: int = 1, *,
                                    compat_q1: bool = True, trim: bool = True,
-                                   capacity: Optional[int] = None, status: Optional[torch.Tensor] = None
-                                   ) -> Tuple[torch.Tensor, torch.Tensor]:
+                                   capacity: Optional[int] = None, status: Optional[torch.Tensor] = None,
+                                   chunk_tiles: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
     """Select key columns per pooled query row.  Returns ``(column_count (B,H,nq) int32,
     column_index (B,H,nq,n) int32)`` with each row's first ``count`` entries valid and ascending.
 
     ``trim=True`` slices ``column_index`` to the largest count like the reference does (this reads
     the maximum back to the host); ``trim=False`` returns the full ``capacity``-wide buffer with
     no synchronisation.  Entries past a row's count are uninitialised (the reference zero-fills).
-    ``k`` may have fewer heads than ``avg_q_chunk`` (grouped-query attention).
+    ``k`` may have fewer heads than ``avg_q_chunk`` (grouped-query attention).  ``chunk_tiles > 0``:
+    the pooled rows span several prefill chunks of that many query tiles, and the causal rule's
+    ``compat_q1`` rows restart at every chunk boundary, as in the reference's chunk loop.
     """
     dev = _require_cuda(avg_q_chunk, k)
     b, h, nq, d = avg_q_chunk.shape
@@ -147,7 +149,7 @@ def fuse_qk_softmax_minp_wo_causal(avg_q_chunk: torch.Tensor, k: torch.Tensor, a
                         int(avg_q_chunk_offset), avg_q_chunk.data_ptr(), _t4(k), gapf,
                         gaps.data_ptr() if gaps is not None else None, gstride,
                         count.data_ptr(), index.data_ptr(), cap,
-                        status.data_ptr() if status is not None else None, 0, None, 0)
+                        status.data_ptr() if status is not None else None, int(chunk_tiles), None, 0)
     if avg_q_chunk.dtype != k.dtype:
         raise VecAttentionArgumentError("pooled queries and keys must have the same dtype")
     nbytes = C.c_size_t(0)
@@ -181,7 +183,10 @@ def sparse_attn_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_poolin
 
 
 def _sparse_attn_bhsd(q, k, v, pq, block_count, block_offset, column_count, column_index, causal,
-                      q_offset=0, softmax_scale=None, out=None, out_layout="bhsd", status=None, lse=None):
+                      q_offset=0, softmax_scale=None, out=None, out_layout="bhsd", status=None, lse=None,
+                      vision: Optional[Tuple[int, int]] = None):
+    """``vision = (begin, end)``: the vision-slice composition in one launch: the tables describe the query
+    tiles of rows [0, end) only; rows before ``begin`` and from ``end`` on get full causal attention."""
     dev = _require_cuda(q, k, v, column_count, column_index)
     b, h, sq, d = q.shape
     hkv, sk = k.shape[1], k.shape[2]
@@ -192,7 +197,7 @@ def _sparse_attn_bhsd(q, k, v, pq, block_count, block_offset, column_count, colu
         else:
             out = torch.empty(b, h, sq, d, dtype=q.dtype, device=dev)
     column_count = column_count.contiguous()
-    nq = math.ceil(sq / pq)
+    nq = math.ceil((sq if vision is None else vision[1]) / pq)
     if tuple(column_count.shape) != (b, h, nq) or tuple(column_index.shape[:3]) != (b, h, nq):
         raise VecAttentionArgumentError("column tables must be shaped (B, H, ceil(Sq/q_pooling_size)[, n])")
     # the index table may be a trimmed view of a wider buffer: pass its row stride instead of copying
@@ -212,7 +217,8 @@ def _sparse_attn_bhsd(q, k, v, pq, block_count, block_offset, column_count, colu
                       column_count.data_ptr(), column_index.data_ptr(), col_stride,
                       float(softmax_scale) if softmax_scale else 0.0,
                       status.data_ptr() if status is not None else None,
-                      lse.data_ptr() if lse is not None else None)
+                      lse.data_ptr() if lse is not None else None,
+                      0 if vision is None else 1, 0 if vision is None else int(vision[0]), 0 if vision is None else int(vision[1]))
     if lse is not None and (lse.dtype != torch.float32 or not lse.is_contiguous() or tuple(lse.shape) != (b, h, sq)):
         raise VecAttentionArgumentError("lse must be a contiguous float32 tensor shaped (B, H, Sq)")
     with torch.cuda.device(dev):

@@ -157,6 +157,10 @@ int va_sparse_attn(const va_attn_args* a, va_stream_t stream) {
   if (a->heads % a->kv_heads != 0 || a->heads > 65535 || a->batch > 65535) return VA_ERR_SHAPE;
   if (a->pq != 64 && a->pq != 128) return VA_ERR_PARAM;
   if (a->q_offset < 0 || a->col_stride <= 0) return VA_ERR_SHAPE;
+  if (a->vision_mode) {  // spattn/src/models/utils.py:97: causal only; one sequence for queries and keys
+    if (a->pq != 64 || !a->causal || a->sq != a->sk || a->q_offset != 0) return VA_ERR_PARAM;
+    if (a->vision_begin < 0 || a->vision_begin > a->vision_end || a->vision_end > a->sq) return VA_ERR_SHAPE;
+  }
   if (int rc = check_tensor(a->q)) return rc;
   if (int rc = check_tensor(a->k)) return rc;
   if (int rc = check_tensor(a->v)) return rc;

@@ -21,7 +21,8 @@ int sparse_attn(const va_attn_args& a, cudaStream_t stream) {
   p.status = a.status;
   p.lse = a.lse;
   p.heads = a.heads; p.rep = a.heads / a.kv_heads; p.sq = a.sq; p.sk = a.sk;
-  p.nq = (a.sq + a.pq - 1) / a.pq;
+  p.vis_on = a.vision_mode != 0; p.vis_begin = a.vision_begin; p.vis_end = a.vision_end;
+  p.nq = ((p.vis_on ? a.vision_end : a.sq) + a.pq - 1) / a.pq;
   p.causal = a.causal; p.q_offset = a.q_offset;
   const float scale = a.softmax_scale > 0.f ? a.softmax_scale : 0.08838834764831845f;
   p.scale_log2 = scale * 1.4426950408889634f;

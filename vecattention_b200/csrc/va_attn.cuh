@@ -22,6 +22,10 @@ struct AttnParams {
   int heads, rep, sq, sk, nq;
   int causal, q_offset;
   float scale_log2;  // softmax_scale * log2(e)
+  // Vision-slice composition (64-row kernel only): rows [0, vis_begin) and [vis_end, sq) get full causal attention
+  // from tiles that need no tables, rows [vis_begin, vis_end) the sparse attention of their tile; `nq` then counts
+  // the table tiles (rows [0, vis_end)) and the grid has the dense tiles behind them.
+  int vis_on, vis_begin, vis_end;
 };
 
 }  // namespace va

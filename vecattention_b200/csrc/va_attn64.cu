@@ -89,7 +89,8 @@ __device__ __forceinline__ void umma_ws(uint32_t d_tmem, uint64_t a_desc, uint64
       : "memory");
 }
 
-template <int DT>
+// VIS: the vision-slice composition (a kernel of its own, so that the ordinary one carries none of its bookkeeping)
+template <int DT, bool VIS>
 __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnParams p) {
   using T = typename Elem<DT>::T;
   constexpr int PQ = 64;
@@ -107,8 +108,33 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   // causal tiles grow with their index: the longest are started first, so the grid's tail is made of short ones
   const int tile = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int hkv = h / p.rep;
-  const int row0 = tile * PQ;
-  const int64_t trow = ((int64_t)b * p.heads + h) * p.nq + tile;
+  // The tile's rows [row0, row_end).  Ordinarily tile t has rows 64 t ... ; in the vision-slice composition the
+  // first p.nq tiles are the sparse tiles of rows [0, vis_end), cut to the rows from vis_begin on, and behind
+  // them come dense tiles for rows [0, vis_begin) and for rows [vis_end, sq): all 64-key blocks up to the
+  // tile's last row, no tables.
+  int row0 = tile * PQ, row_end_v = 0;
+  bool dense = false;
+  if constexpr (VIS) {
+    int row_end = min(row0 + PQ, p.sq);
+    if (tile < p.nq) {
+      row_end = min(row0 + PQ, p.vis_end);
+      row0 = max(row0, p.vis_begin);
+    } else {
+      dense = true;
+      const int e = tile - p.nq, n_before = (p.vis_begin + PQ - 1) / PQ;
+      if (e < n_before) {
+        row0 = e * PQ;
+        row_end = min(row0 + PQ, p.vis_begin);
+      } else {
+        row0 = p.vis_end + (e - n_before) * PQ;
+        row_end = min(row0 + PQ, p.sq);
+      }
+    }
+    if (row_end <= row0) return;  // every row of this sparse tile belongs to the dense part before it
+    row_end_v = row_end;
+  }
+  const int row_end = VIS ? row_end_v : p.sq;  // rows of the tile at or past it do not exist (a tile has at most 64)
+  const int64_t trow = (VIS && dense) ? 0 : ((int64_t)b * p.heads + h) * p.nq + tile;
 
   unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
   unsigned char* q_s = smem;
@@ -119,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   // The start of a tile is a chain of memory latencies (counts -> indices -> rows -> first product).  What only
   // depends on the tile's position is requested before the counts are known: the Q tile, and the first two chunks'
   // column indices (speculatively: a tile with dense blocks, which come first in slot order, fetches again).
-  const int32_t* blk = p.blk_idx + trow * p.blk_stride;
+  const int32_t* blk = (VIS && dense) ? nullptr : p.blk_idx + trow * p.blk_stride;  // no table: blocks 0, 64, 128, ...
   const int32_t* col = p.col_idx + trow * p.col_stride;
   int raw_first = 0, raw_second = 0;
   if (warp >= 8 && warp < 16) {
@@ -129,16 +155,16 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
 #pragma unroll
       for (int i = 0; i < 8; ++i) {  // Q tile: rows beyond the sequence are zero
         const int pce = pt + i * 128, r = pce >> 4, c = pce & 15;
-        const bool ok = row0 + r < p.sq;
+        const bool ok = row0 + r < row_end;
         cp_async16(smem_addr(q_s + tile_off(64, r, c)), qb + (int64_t)(ok ? row0 + r : 0) * p.q_ss + c * 8, ok);
       }
     }
     const int my_slot = 2 * (warp & 3) + (lane >> 4) + 8 * (lane & 15);
-    if (my_slot < p.col_stride) raw_first = ldg_nc(col + my_slot);
-    if (kChunk + my_slot < p.col_stride) raw_second = ldg_nc(col + kChunk + my_slot);
+    if (!(VIS && dense) && my_slot < p.col_stride) raw_first = ldg_nc(col + my_slot);
+    if (!(VIS && dense) && kChunk + my_slot < p.col_stride) raw_second = ldg_nc(col + kChunk + my_slot);
   }
-  const int nblk = p.blk_count ? __ldg(p.blk_count + trow) : 0;
-  const int ncol = __ldg(p.col_count + trow);
+  const int nblk = (VIS && dense) ? (row_end - 1) / 64 + 1 : (p.blk_count ? __ldg(p.blk_count + trow) : 0);
+  const int ncol = (VIS && dense) ? 0 : __ldg(p.col_count + trow);
   const int nslots = nblk * 64 + ncol;
   const int nchunks = (nslots + kChunk - 1) / kChunk;
   T* ob = static_cast<T*>(p.out) + b * p.o_sb + h * p.o_sh;
@@ -146,9 +172,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
   if (nchunks == 0) {  // no key at all: the tile's output is zero
     for (int i = tid; i < PQ * 16; i += kThreads) {
       const int r = i >> 4, c = i & 15;
-      if (row0 + r < p.sq) *reinterpret_cast<uint4*>(ob + (int64_t)(row0 + r) * p.o_ss + c * 8) = make_uint4(0, 0, 0, 0);
+      if (row0 + r < row_end) *reinterpret_cast<uint4*>(ob + (int64_t)(row0 + r) * p.o_ss + c * 8) = make_uint4(0, 0, 0, 0);
     }
-    if (p.lse && tid < PQ && row0 + tid < p.sq) p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + tid] = -INFINITY;
+    if (p.lse && tid < PQ && row0 + tid < row_end) p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + tid] = -INFINITY;
     cp_async_commit();
     cp_async_wait<0>();  // the Q copies requested above must not outlive the CTA
     return;
@@ -156,6 +182,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
 
   auto fetch_raw = [&](int j, int my_slot) -> int {
     const int slot = j * kChunk + my_slot;
+    if (VIS && slot < nblk * 64 && blk == nullptr) return (slot >> 6) << 6;  // a dense tile: block i starts at key 64 i
     const int ci = min(max(slot - nblk * 64, 0), max(ncol - 1, 0));
     return ldg_nc(slot < nblk * 64 ? blk + (slot >> 6) : col + ci);
   };
@@ -440,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
       if (mbar_wait(&bars.fin, 0)) {
         l = (fin_s[tl] + fin_s[tl ^ 64]) + (fin_s[128 + tl] + fin_s[128 + (tl ^ 64)]);
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        const bool row_ok = row0 + row < p.sq;
+        const bool row_ok = row0 + row < row_end;
         if (p.lse && row_ok && grp == 0 && half == 0)  // one of the row's four owners; m is in the exp2 domain
           p.lse[((int64_t)b * p.heads + h) * p.sq + row0 + row] = l > 0.f ? (m_fin + log2f(l)) * 0.6931471805599453f : -INFINITY;
         // the two groups split the 64 columns of a lane: group 0 writes the lower 32, group 1 the upper
@@ -473,11 +500,12 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
 template <int DT>
 int launch(const AttnParams& p, int batch, cudaStream_t stream) {
   // per-device attribute; setting it on every launch keeps multi-device processes correct
-  if (cudaFuncSetAttribute(sparse_attn64_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) !=
-      cudaSuccess)
-    return VA_ERR_CUDA;
-  dim3 grid(p.nq, p.heads, batch);
-  sparse_attn64_kernel<DT><<<grid, kThreads, kSmem, stream>>>(p);
+  auto kern = p.vis_on ? sparse_attn64_kernel<DT, true> : sparse_attn64_kernel<DT, false>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess) return VA_ERR_CUDA;
+  int tiles = p.nq;
+  if (p.vis_on) tiles += (p.vis_begin + 63) / 64 + (p.sq - p.vis_end + 63) / 64;  // the dense tiles before and after
+  dim3 grid(tiles, p.heads, batch);
+  kern<<<grid, kThreads, kSmem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
 }
 

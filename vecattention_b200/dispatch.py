@@ -35,6 +35,10 @@ def Full_prefill(query_states: torch.Tensor, key_states: torch.Tensor, value_sta
     q_off = sk - sq if causal else 0
     if causal and q_off < 0:
         raise VecAttentionArgumentError("causal dense attention needs at least as many keys as queries")
+    if causal and q_off == 0:  # every tile is a table-free dense tile of the kernel's vision-slice mode
+        none = torch.zeros(b, h, nq, dtype=torch.int32, device=dev)
+        return _sparse_attn_bhsd(query_states, key_states, value_states, 64, None, None, none,
+                                 torch.zeros(b, h, nq, 4, dtype=torch.int32, device=dev), True, vision=(sq, sq))
     last_key = (torch.clamp(q_off + (torch.arange(nq, device=dev) + 1) * 64, max=q_off + sq) - 1) if causal else \
         torch.full((nq,), sk - 1, device=dev)
     count = (last_key // 64 + 1).to(torch.int32)

@@ -4,9 +4,11 @@ vision span get full attention, positions up to the end of the vision span get V
 tokens after it get full attention over all keys.
 
 The reference makes three calls (two to its dense flash-attention wrapper) and concatenates.  Here
-every part writes straight into one output tensor, and the dense parts run on the same
-vector-sparse kernel with block tables that list every 64-key block up to the diagonal, so no
-second attention implementation is involved.
+every part writes straight into one output tensor and the dense parts run on the same
+vector-sparse kernel, so no second attention implementation is involved.  With q_pooling_size 64
+all three parts are ONE attention launch: the sparse tiles of the vision span are cut at the span's
+first row, and table-free dense tiles (every 64-key block up to the diagonal) cover the rows before
+and after it.  Otherwise the parts run one after another, the dense ones with explicit block tables.
 """
 from __future__ import annotations
 
@@ -15,7 +17,8 @@ from typing import Optional, Tuple, Union
 
 import torch
 
-from .api import VecAttention_prefill, VecAttentionArgumentError, _sparse_attn_bhsd
+from .api import (VecAttention_prefill, VecAttentionArgumentError, _sparse_attn_bhsd, average_vector, block_tables,
+                  fuse_qk_softmax_minp_wo_causal)
 
 _DENSE_TILE = 64  # query rows per tile of the dense passes
 
@@ -62,11 +65,16 @@ def VecAttention_prefill_vision(
     vision_end_position: Optional[int] = None,
     *,
     compat_q1: bool = True,
+    fused: Optional[bool] = None,
 ) -> torch.Tensor:
     """The ``vecattention`` branch of the reference's ``customize_prefill_attention``: with both
     positions ``None`` plain ``VecAttention_prefill``; otherwise (causal only) full attention for
     rows before ``vision_start_position``, VecAttention over ``[0, vision_end_position)`` and full
-    attention over all keys for rows from ``vision_end_position`` on.  Returns (B,H,S,D)."""
+    attention over all keys for rows from ``vision_end_position`` on.  Returns (B,H,S,D).
+
+    ``fused`` (default: whenever ``q_pooling_size`` is 64 and the index lists fit 4 GiB): one attention
+    launch serves all three parts: sparse tiles for the vision span, cut at ``vision_start_position``,
+    and table-free dense tiles before and after it; ``False`` runs the three parts one after another."""
     vs, ve = vision_start_position, vision_end_position
     if vs is None and ve is None:
         return VecAttention_prefill(query_states, key_states, value_states, threshold, q_pooling_size, k_local_size,
@@ -79,6 +87,27 @@ def VecAttention_prefill_vision(
     end = s if ve is None else max(0, min(int(ve), s))
     begin = 0 if vs is None else max(0, min(int(vs), end))
     out = torch.empty_like(query_states)
+    if fused is None:
+        fused = q_pooling_size == 64 and b * h * math.ceil(max(end, 1) / 64) * ((end + 3) // 4 * 4) * 4 <= (4 << 30)
+    if fused and q_pooling_size != 64:
+        raise VecAttentionArgumentError("the one-launch composition needs q_pooling_size 64")
+    if fused and end > begin:
+        # pooling and selection over rows [0, end) exactly as VecAttention_prefill runs them (its chunk loop only
+        # shows in the rows the causal rule treats specially), then one attention launch over all rows
+        if threshold is None:
+            raise VecAttentionArgumentError("threshold is required")
+        gap = -torch.log(threshold.to(query_states.device) + 1e-9) if isinstance(threshold, torch.Tensor) \
+            else -math.log(threshold + 1e-9, math.e)
+        if chunk_size % q_pooling_size != 0:
+            raise VecAttentionArgumentError("chunk_size must be a multiple of q_pooling_size")
+        avg = average_vector(query_states[:, :, :end], 64)
+        cnt, idx = fuse_qk_softmax_minp_wo_causal(avg, key_states[:, :, :end], 0, gap, True, 64, k_local_size,
+                                                  wo_initial=True, group_k_block=group_k_block, compat_q1=compat_q1,
+                                                  trim=False, chunk_tiles=chunk_size // 64)
+        bcnt, bidx = block_tables(b, h, end, 64, True, query_states.device)
+        _sparse_attn_bhsd(query_states, key_states, value_states, 64, bcnt, bidx, cnt, idx, True, out=out,
+                          vision=(begin, end))
+        return out
     if end > 0:  # VecAttention on [0, end); the rows before `begin` are overwritten below
         VecAttention_prefill(query_states[:, :, :end], key_states[:, :, :end], value_states[:, :, :end], threshold,
                              q_pooling_size, k_local_size, group_k_block, True, chunk_size, compat_q1=compat_q1,
