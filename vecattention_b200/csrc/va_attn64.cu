@@ -259,10 +259,22 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
     {
       int keys[16];
       int raw0 = raw_first, raw1 = raw_second;
+      // a tile without dense blocks (every non-causal tile): slot s is entry s of the column list
+      const bool plain = nblk == 0;
+      int stage = 0;           // ring position of chunk j, and how often the ring has gone round (mod 2)
+      uint32_t round = 0;
       for (int j = 0; j < nchunks && !timed_out; ++j) {
-        const int key = decode(j, raw0);
-        raw0 = raw1;
-        if (j + 2 < nchunks) raw1 = fetch_raw(j + 2, my_slot);
+        int key;
+        if (plain) {
+          const int slot = j * kChunk + my_slot;
+          key = (slot < ncol && (unsigned)raw0 < (unsigned)p.sk) ? raw0 : -1;
+          raw0 = raw1;
+          if (j + 2 < nchunks) raw1 = ldg_nc(col + min(slot + 2 * kChunk, ncol - 1));
+        } else {
+          key = decode(j, raw0);
+          raw0 = raw1;
+          if (j + 2 < nchunks) raw1 = fetch_raw(j + 2, my_slot);
+        }
         if (!is_v) {
           keys_s[j & 7][my_slot] = key;
           // unused slots, and keys that some row of the tile may not see, make the chunk take the masking pass
@@ -272,13 +284,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn64_kernel(const AttnPa
         }
         spread(j, key, keys);
         if (!is_v) {
-          const int ks = j % kKStages, ku = j / kKStages;
-          if (!mbar_wait(&bars.kempty[ks], (ku & 1) ^ 1)) { timed_out = true; break; }
-          copy_tile(k_s + (size_t)ks * kKvTile, kb, p.k_ss, keys, &bars.kfull[ks]);
+          if (!mbar_wait(&bars.kempty[stage], round ^ 1)) { timed_out = true; break; }
+          copy_tile(k_s + (size_t)stage * kKvTile, kb, p.k_ss, keys, &bars.kfull[stage]);
+          if (++stage == kKStages) { stage = 0; round ^= 1; }
         } else {
-          const int vs = j % kVStages, vu = j / kVStages;
-          if (!mbar_wait(&bars.vempty[vs], (vu & 1) ^ 1)) { timed_out = true; break; }
-          copy_tile(v_s + (size_t)vs * kKvTile, vb, p.v_ss, keys, &bars.vfull[vs]);
+          if (!mbar_wait(&bars.vempty[stage], round ^ 1)) { timed_out = true; break; }
+          copy_tile(v_s + (size_t)stage * kKvTile, vb, p.v_ss, keys, &bars.vfull[stage]);
+          if (++stage == kVStages) { stage = 0; round ^= 1; }
         }
       }
     }
