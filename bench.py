@@ -340,6 +340,11 @@ def _rooflines(wl, peaks, stage, flops, counts):
                                  "algorithmic 4.6 GB, K/V of two 61 MB heads do not both stay in the 126 MB L2" if traffic else
                                  "not captured for this workload or head count"),
                 "peak_source": peaks["_source"] + " burst"}
+    if peaks.get("bf16_tflops_sustained"):
+        # the kernel runs for tens of milliseconds back to back under the power cap (see `clocks`): the denominator a
+        # seconds-long GEMM loop reaches is given beside the burst figure; `frac` stays the fraction of the burst peak
+        roofline["peak_sustained"] = peaks["bf16_tflops_sustained"]
+        roofline["frac_of_sustained"] = achieved_tf / peaks["bf16_tflops_sustained"]
     sel_gbs = sel_bytes / ((stage["pool_ms"] + stage["select_ms"]) * 1e-3) / 1e9
     est_flops = 2.0 * wl.nq * wl.seq_len * D * wl.heads * wl.batch * (0.5 if wl.causal else 1.0)
     roofline_select = {"kernel": "pool_q_kernel+select_mask_kernel+select_expand_kernel", "bound": "hbm", "achieved": sel_gbs,
