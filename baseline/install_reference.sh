@@ -1,7 +1,7 @@
 #!/bin/bash
 # Install the unmodified reference (anminliu/VecAttention) into baseline/_ref, offline.
 #
-#   baseline/install_reference.sh [/path/to/VecAttention]      (default /root/reference)
+#   baseline/install_reference.sh /path/to/VecAttention        (or VECATTENTION_REFERENCE=/path/to/VecAttention)
 #
 # pip builds a wheel from a scratch copy (the checkout may be read-only) and unpacks it into
 # baseline/_ref, which is git-ignored.  No dependency is resolved (--no-deps): the image supplies
@@ -10,7 +10,8 @@
 # wheel lacks them; they are copied beside the installed kernels, where the code looks for them
 # (spattn/src/kernels/vecattention_kernels.py:21).
 set -euo pipefail
-SRC=${1:-/root/reference}
+SRC=${1:-${VECATTENTION_REFERENCE:-}}
+if [ -z "$SRC" ] || [ ! -d "$SRC/spattn" ]; then echo "usage: $0 /path/to/VecAttention" >&2; exit 2; fi
 HERE=$(cd "$(dirname "$0")" && pwd)
 TMP=$(mktemp -d)
 cp -r "$SRC"/. "$TMP"/
