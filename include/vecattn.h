@@ -271,6 +271,27 @@ typedef struct {
 } va_norm_rope_args;
 int va_qk_norm_rope(const va_norm_rope_args* args, va_stream_t stream);
 
+/* The same preparation where the tensors are (B,H,L,128) already and the norm is per head (HunyuanVideo,
+ * eval/DiTEvalKit/models/hyvideo/attention.py:187-213): replaces rms_norm_forward on the rows of 128 elements
+ * (eval/DiTEvalKit/kernels/csrc/ops.h:52-74, include/norm/narrow_rms_norm.cuh) and
+ * apply_qk_rope_inplace_cossin_txtlast (csrc/ops.h:146, include/rope/rope_enc_txtlast.cuh) by one pass.
+ *   q, k          (B,H,L,128) / (B,Hkv,L,128), any 16-byte aligned strides; q_out, k_out may be the inputs
+ *   q_weight, k_weight  128 elements of the tensors' dtype; NULL skips the norm
+ *   cos, sin      (rope_len, 128) float32, per element; NULL for no rotation.  Tokens l < rope_len are rotated
+ *                 (the text tokens come last): out[i] = y[i] cos[l,i] + (i even ? -y[i+1] : y[i-1]) sin[l,i], fp32.
+ * y = T((x * rsqrt(sum(x^2)/128 + eps)) * w). */
+typedef struct {
+  int32_t dtype, batch, seq_len, heads, kv_heads, rope_len;
+  va_tensor4 q, k;
+  va_tensor4_out q_out, k_out;
+  const void* q_weight;
+  const void* k_weight;
+  float eps;
+  const float* cos;
+  const float* sin;
+} va_head_norm_rope_args;
+int va_qk_head_norm_rope(const va_head_norm_rope_args* args, va_stream_t stream);
+
 const char* va_status_string(int code);
 int va_version(void);
 

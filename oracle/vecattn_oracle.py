@@ -463,3 +463,23 @@ def rope_interleaved(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, skip
     rot = torch.stack((e * c - o * s, o * c + e * s), dim=-1).flatten(-2)
     out[:, :, skip:] = _round_from_double(rot, x.dtype)
     return out
+
+
+def rope_interleaved_txtlast(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, txt_len: int = 0) -> torch.Tensor:
+    """Rotary embedding of (B, H, L, D) on interleaved pairs with per-element float32 tables (L - txt_len, D),
+    computed in float32 as the reference's text-last kernel does through flashinfer's helper
+    (eval/DiTEvalKit/kernels/include/rope/rope_enc_txtlast.cuh:32-76; flashinfer/pos_enc.cuh
+    ``vec_apply_llama_rope_cos_sin_interleave``): out[i] = x[i] cos[i] + (-x[i+1] if i even else x[i-1]) sin[i];
+    the last ``txt_len`` tokens are not rotated.  (The product pair is evaluated here as
+    ``other * sin + fl(x * cos)``; a fused or unfused choice there moves a result by one float32 unit at most.)"""
+    out = x.clone()
+    n = x.shape[2] - txt_len
+    if n <= 0:
+        return out
+    xf = x[:, :, :n].float()
+    other = torch.stack((-xf[..., 1::2], xf[..., 0::2]), dim=-1).flatten(-2)
+    first = (xf * cos.float()).double()                       # fl(x cos), exact in double
+    rot = (other.double() * sin.double() + first).float()     # one rounding of other * sin + fl(x cos): the fused form
+    out[:, :, :n] = rot.to(x.dtype)
+    return out
+

@@ -38,6 +38,7 @@ def test_struct_layout_matches_header(lib):
     assert C.sizeof(lib.SelectArgs) == 56 + 8 + 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8
     assert C.sizeof(lib.AttnArgs) == 40 + 4 * 32 + 8 * 6 + 8 + 8 + 8 + 16   # ... + three int32 and padding
     assert C.sizeof(lib.NormRopeArgs) == 24 + 8 * 8 + 8 * 2 + 8 + 8 + 8
+    assert C.sizeof(lib.HeadNormRopeArgs) == 24 + 4 * 32 + 8 * 2 + 8 + 8 * 2
     assert C.sizeof(lib.PrefillArgs) == 56 + 4 * 32 + 8 + 8 + 8 + 8 + 8 + 8 + 8 + 8
 
 

@@ -92,3 +92,60 @@ def test_operator_reads_the_prepared_layout_in_place(built_library):
     out = va.VecAttention_prefill(qh, kh, vh, 0.6, 64, 16, 8192, False, 32768)
     ref = va.VecAttention_prefill(qh.contiguous(), kh.contiguous(), vh.contiguous(), 0.6, 64, 16, 8192, False, 32768)
     assert torch.equal(out, ref)
+
+
+def test_oracle_txtlast_rope_is_the_rotation_when_pairs_share_an_angle():
+    """Per-element tables whose two entries of a pair carry the same angle (how the reference's callers fill
+    them) turn the text-last formula into the plain rotation of the pair; the text tokens stay as they are."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(1, 2, 50, 128, generator=g).to(torch.bfloat16)
+    c64, s64 = _tables(40, 128, 6)
+    cos, sin = c64.repeat_interleave(2, dim=1).contiguous(), s64.repeat_interleave(2, dim=1).contiguous()
+    got = O.rope_interleaved_txtlast(x, cos, sin, txt_len=10)
+    want = O.rope_interleaved(x[:, :, :40], c64, s64)
+    assert torch.equal(got[:, :, 40:], x[:, :, 40:])
+    step = want.float().abs().clamp_min(2.0 ** -6) * 2.0 ** -7
+    assert bool(((got[:, :, :40].float() - want.float()).abs() <= step).all())   # float32 against double arithmetic
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,heads,kv_heads,l,txt", [(1, 24, 24, 1000, 256), (2, 6, 2, 333, 0), (1, 3, 3, 17, 17), (1, 2, 1, 64, 5)])
+def test_head_norm_and_txtlast_rope_match_oracle(built_library, dtype, b, heads, kv_heads, l, txt):
+    """The per-head preparation (RMSNorm over 128 elements, rotary embedding on all but the last text tokens) against
+    the oracle; parity unpinned: the reference's CUDA extension for these two ops is not built here."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from vecattention_b200.preattn import qk_head_norm_rope
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(b, heads, l, 128, generator=g).to(dtype)
+    k = torch.randn(b, kv_heads, l, 128, generator=g).to(dtype)
+    wq = (1 + 0.1 * torch.randn(128, generator=g)).to(dtype)
+    wk = (1 + 0.1 * torch.randn(128, generator=g)).to(dtype)
+    ang = torch.rand(max(l - txt, 1), 128, generator=g) * 6.283
+    cos, sin = torch.cos(ang).float().contiguous(), torch.sin(ang).float().contiguous()
+    qg, kg = qk_head_norm_rope(q.cuda(), k.cuda(), wq.cuda(), wk.cuda(), 1e-6, cos.cuda(), sin.cuda(), txt)
+    tiny = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    for got, x, w in ((qg, q, wq), (kg, k, wk)):
+        ref = O.rope_interleaved_txtlast(O.rms_norm(x, w, 1e-6), cos[: l - txt], sin[: l - txt], txt)
+        diff = got.cpu() != ref
+        # the approximate reciprocal square root and the order of the sum may move a normalised element to the
+        # neighbouring 16-bit value, and with it the two rotated results of its pair
+        assert diff.float().mean() <= 2e-2, diff.float().mean().item()
+        rf = ref.float()
+        mag = (rf[..., 0::2] ** 2 + rf[..., 1::2] ** 2).sqrt().repeat_interleave(2, dim=-1).clamp_min(1e-3)
+        assert bool(((got.cpu().float() - rf).abs() <= 3.01 * mag * tiny).all())
+    # the text tokens are normalised but not rotated; rotation only is exact; in place
+    if txt:
+        assert torch.equal(qg[:, :, l - txt:].cpu(), qk_head_norm_rope(q.cuda(), k.cuda(), wq.cuda(), wk.cuda(), 1e-6)[0][:, :, l - txt:].cpu())
+    qr, kr = qk_head_norm_rope(q.cuda(), k.cuda(), None, None, 0.0, cos.cuda(), sin.cuda(), txt)
+    assert torch.equal(qr.cpu(), O.rope_interleaved_txtlast(q, cos[: l - txt], sin[: l - txt], txt))
+    assert torch.equal(kr.cpu(), O.rope_interleaved_txtlast(k, cos[: l - txt], sin[: l - txt], txt))
+    qd, kd = q.cuda(), k.cuda()
+    qi, ki = qk_head_norm_rope(qd, kd, wq.cuda(), wk.cuda(), 1e-6, cos.cuda(), sin.cuda(), txt, inplace=True)
+    assert qi.data_ptr() == qd.data_ptr() and torch.equal(qi, qg) and torch.equal(ki, kg)
+    # strided input (a slice of a longer sequence, as the two-stream blocks pass it)
+    big = torch.randn(b, heads, l + 8, 128, generator=g).to(dtype).cuda()
+    qs, _ = qk_head_norm_rope(big[:, :, 3: 3 + l], k.cuda(), wq.cuda(), wk.cuda(), 1e-6, cos.cuda(), sin.cuda(), txt)
+    qc, _ = qk_head_norm_rope(big[:, :, 3: 3 + l].contiguous(), k.cuda(), wq.cuda(), wk.cuda(), 1e-6, cos.cuda(), sin.cuda(), txt)
+    assert torch.equal(qs, qc)

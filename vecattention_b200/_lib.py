@@ -17,7 +17,7 @@ VA_STATUS_TIMEOUT = 2
 # every symbol include/vecattn.h declares
 EXPORTS = ("va_pool_q", "va_select", "va_select_workspace_bytes", "va_sparse_attn", "va_sparse_attn_workspace_bytes",
            "va_block_tables", "va_prefill_workspace_bytes", "va_prefill", "va_prefill_static", "va_prefill_static_fits",
-           "va_selftest_wait_timeout", "va_qk_norm_rope", "va_status_string", "va_version")
+           "va_selftest_wait_timeout", "va_qk_norm_rope", "va_qk_head_norm_rope", "va_status_string", "va_version")
 VA_SINGLE_PASS_INDEX_BYTES_DEFAULT = 4 << 30
 VA_STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -74,6 +74,14 @@ class NormRopeArgs(C.Structure):
                 ("cos", C.c_void_p), ("sin", C.c_void_p)]
 
 
+class HeadNormRopeArgs(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("batch", C.c_int32), ("seq_len", C.c_int32), ("heads", C.c_int32),
+                ("kv_heads", C.c_int32), ("rope_len", C.c_int32),
+                ("q", Tensor4), ("k", Tensor4), ("q_out", Tensor4), ("k_out", Tensor4),
+                ("q_weight", C.c_void_p), ("k_weight", C.c_void_p), ("eps", C.c_float),
+                ("cos", C.c_void_p), ("sin", C.c_void_p)]
+
+
 _LIB = None
 
 
@@ -102,6 +110,7 @@ def lib() -> C.CDLL:
     handle.va_prefill_static_fits.argtypes = [C.POINTER(PrefillArgs)]
     handle.va_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
     handle.va_qk_norm_rope.argtypes = [C.POINTER(NormRopeArgs), C.c_void_p]
+    handle.va_qk_head_norm_rope.argtypes = [C.POINTER(HeadNormRopeArgs), C.c_void_p]
     for name in EXPORTS:
         getattr(handle, name).restype = C.c_int
     handle.va_status_string.argtypes = [C.c_int]

@@ -9,6 +9,7 @@ int select(const va_select_args& a, cudaStream_t stream);
 size_t select_workspace_bytes(int batch, int heads, int kv_heads, int nq, int sk);
 int sparse_attn(const va_attn_args& a, cudaStream_t stream);
 int qk_norm_rope(const va_norm_rope_args& a, cudaStream_t stream);
+int qk_head_norm_rope(const va_head_norm_rope_args& a, cudaStream_t stream);
 
 // dense-block tables of query tiles [tile_off, tile_off + nqc) written as a contiguous (BH, nqc) slice
 __global__ void block_tables_kernel(int bh, int seq_len, int pq, int causal, int tile_off, int nqc,
@@ -180,6 +181,22 @@ int va_qk_norm_rope(const va_norm_rope_args* a, va_stream_t stream) {
     if (p && !aligned16(p)) return VA_ERR_ALIGN;
   if (a->q_row_stride % 8 || a->k_row_stride % 8 || a->q_out_row_stride % 8 || a->k_out_row_stride % 8) return VA_ERR_ALIGN;
   return qk_norm_rope(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int va_qk_head_norm_rope(const va_head_norm_rope_args* a, va_stream_t stream) {
+  if (!a || !a->q.ptr || !a->k.ptr || !a->q_out.ptr || !a->k_out.ptr) return VA_ERR_NULL;
+  if ((a->cos == nullptr) != (a->sin == nullptr)) return VA_ERR_NULL;
+  if (a->dtype != VA_BF16 && a->dtype != VA_FP16) return VA_ERR_DTYPE;
+  if (a->batch <= 0 || a->seq_len <= 0 || a->heads <= 0 || a->kv_heads <= 0) return VA_ERR_SHAPE;
+  if (a->rope_len < 0 || a->rope_len > a->seq_len) return VA_ERR_SHAPE;
+  if (int rc = check_tensor(a->q)) return rc;
+  if (int rc = check_tensor(a->k)) return rc;
+  if (int rc = check_tensor(a->q_out)) return rc;
+  if (int rc = check_tensor(a->k_out)) return rc;
+  const void* ptrs[] = {a->q_weight, a->k_weight, a->cos, a->sin};
+  for (const void* p : ptrs)
+    if (p && !aligned16(p)) return VA_ERR_ALIGN;
+  return qk_head_norm_rope(*a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int va_block_tables(int32_t batch, int32_t heads, int32_t seq_len, int32_t pq, int32_t causal, int32_t* blk_count,

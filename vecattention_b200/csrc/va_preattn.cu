@@ -6,20 +6,19 @@
 // three transposed copies to (B, H, S, D) (read + write each) and an in-place rotary kernel (read + write).
 // Here every element of Q and K is read once and written once; V is not touched.
 //
-// One CTA of 256 threads per token row of one tensor (grid.y: 0 = Q, 1 = K).  A thread owns 16-byte pieces
-// (8 elements) of the row: sum of squares in fp32 (per thread in element order, then a fixed shuffle tree and a
-// fixed sum over the warps), y = round16(x * rstd * w) as the norm kernel stores it
+// A token row of one tensor (grid.y: 0 = Q, 1 = K) is taken by one, two or four warps, whose lanes own 16-byte
+// pieces (8 elements) of it: sum of squares in fp32 (per lane in piece order, a fixed shuffle tree, a fixed sum over
+// the row's warps), y = round16(x * rstd * w) as the norm kernel stores it
 // (eval/DiTEvalKit/kernels/triton/rmsnorm.py:30-47), then out = round16(double(y0) * cos - double(y1) * sin),
 // round16(double(y1) * cos + double(y0) * sin) for every pair, in double precision as the rotary kernel
 // computes it (eval/DiTEvalKit/kernels/include/rope/rope_enc_complex.cuh:27-45).
+// A second kernel serves models whose tensors are (B, H, L, 128) already, with a per-head norm and the text tokens
+// last (HunyuanVideo).
 #include "va_common.cuh"
 
 namespace va {
 
 namespace {
-
-constexpr int kNormThreads = 256;
-constexpr int kMaxPieces = 4;  // 16-byte pieces per thread: hidden sizes up to 256 * 4 * 8 = 8192 elements
 
 template <int DT>
 __device__ __forceinline__ typename Elem<DT>::T from_double(double x) {
@@ -27,72 +26,81 @@ __device__ __forceinline__ typename Elem<DT>::T from_double(double x) {
   else return __double2half(x);
 }
 
+// ---- the hidden-size form: W warps per token row ------------------------------------------------------------------
+// A row is taken by W = ceil(hidden / 1024) warps; a lane keeps its (up to) four 16-byte pieces packed in registers,
+// so every warp has its whole share of the row in flight at once, and the W warps add their partial sums through
+// shared memory (one block barrier).  Few registers, hence some thirty warps resident per SM: enough outstanding
+// memory, which one CTA per row with one piece or two per thread in flight was not (2.4 TB/s).  A CTA holds as many
+// whole rows as fit eight warps.
+constexpr int NP = 4;  // pieces per lane
 template <int DT>
-__global__ void __launch_bounds__(kNormThreads) qk_norm_rope_kernel(const va_norm_rope_args a) {
+__global__ void __launch_bounds__(256) qk_norm_rope_rows_kernel(const va_norm_rope_args a, int64_t rows, int W, int rows_per_cta) {
   using T = typename Elem<DT>::T;
+  __shared__ float part[8];  // [row of the CTA * W + warp of the row]
   const bool is_k = blockIdx.y == 1;
-  const int64_t token = blockIdx.x;                 // b * seq_len + s
-  const int s = (int)(token % a.seq_len);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rsub = warp / W, wsub = warp % W;
+  const int64_t token = (int64_t)blockIdx.x * rows_per_cta + rsub;  // b * seq_len + s
+  const bool live = token < rows;
+  const int s = (int)((live ? token : 0) % a.seq_len);
   const int hidden = (is_k ? a.kv_heads : a.heads) * kHeadDim;
-  const T* x = static_cast<const T*>(is_k ? a.k : a.q) + token * (is_k ? a.k_row_stride : a.q_row_stride);
-  T* y = static_cast<T*>(is_k ? a.k_out : a.q_out) + token * (is_k ? a.k_out_row_stride : a.q_out_row_stride);
+  const T* x = static_cast<const T*>(is_k ? a.k : a.q) + (live ? token : 0) * (is_k ? a.k_row_stride : a.q_row_stride);
+  T* y = static_cast<T*>(is_k ? a.k_out : a.q_out) + (live ? token : 0) * (is_k ? a.k_out_row_stride : a.q_out_row_stride);
   const T* w = static_cast<const T*>(is_k ? a.k_weight : a.q_weight);
-  const int pieces = hidden / 8;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int pieces = live ? hidden / 8 : 0;
 
-  float v[kMaxPieces][8];
+  uint4 raw[NP];
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    const int pc = wsub * 32 + lane + 32 * W * i;
+    raw[i] = pc < pieces ? __ldg(reinterpret_cast<const uint4*>(x + pc * 8)) : make_uint4(0, 0, 0, 0);
+  }
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxPieces; ++i) {
-    const int pc = tid + i * kNormThreads;
-    if (pc < pieces) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + pc * 8));
-      const uint32_t ww[4] = {raw.x, raw.y, raw.z, raw.w};
+  for (int i = 0; i < NP; ++i) {
+    const uint32_t ww[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = Elem<DT>::unpack(ww[j]);
-        v[i][2 * j] = f.x;
-        v[i][2 * j + 1] = f.y;
-        ss = fmaf(f.x, f.x, ss);
-        ss = fmaf(f.y, f.y, ss);
-      }
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = Elem<DT>::unpack(ww[j]);
+      ss = fmaf(f.x, f.x, ss);
+      ss = fmaf(f.y, f.y, ss);
     }
   }
-  __shared__ float part[kNormThreads / 32];
-  __shared__ float rstd_s;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if (lane == 0) part[warp] = ss;
-  __syncthreads();
-  if (tid == 0) {
-    float tot = 0.f;
-#pragma unroll
-    for (int i = 0; i < kNormThreads / 32; ++i) tot += part[i];
-    rstd_s = 1.0f / sqrtf(tot / (float)hidden + a.eps);
+  if (W > 1) {
+    if (lane == 0) part[rsub * W + wsub] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int i = 0; i < W; ++i) ss += part[rsub * W + i];  // the same order in every warp of the row
   }
-  __syncthreads();
-  const float rstd = w ? rstd_s : 1.0f;  // no weight: no normalisation (rotary embedding only)
+  const float rstd = w ? 1.0f / sqrtf(ss / (float)hidden + a.eps) : 1.0f;  // no weight: no normalisation
 
   const int rs = s - a.rope_skip;  // row of the cos / sin tables; the first rope_skip tokens are not rotated
   const bool rotate = a.cos != nullptr && rs >= 0;
 #pragma unroll
-  for (int i = 0; i < kMaxPieces; ++i) {
-    const int pc = tid + i * kNormThreads;
+  for (int i = 0; i < NP; ++i) {
+    const int pc = wsub * 32 + lane + 32 * W * i;
     if (pc < pieces) {
+      const uint32_t xw[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
       float yv[8];
       if (w) {
         const uint4 wr = __ldg(reinterpret_cast<const uint4*>(w + pc * 8));
         const uint32_t ww[4] = {wr.x, wr.y, wr.z, wr.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float2 f = Elem<DT>::unpack(ww[j]);
+          const float2 f = Elem<DT>::unpack(ww[j]), v = Elem<DT>::unpack(xw[j]);
           // x_hat = x * rstd, y = x_hat * w, rounded to the 16-bit type as the norm kernel stores it
-          yv[2 * j] = Elem<DT>::to_float(Elem<DT>::from_float(__fmul_rn(__fmul_rn(v[i][2 * j], rstd), f.x)));
-          yv[2 * j + 1] = Elem<DT>::to_float(Elem<DT>::from_float(__fmul_rn(__fmul_rn(v[i][2 * j + 1], rstd), f.y)));
+          yv[2 * j] = Elem<DT>::to_float(Elem<DT>::from_float(__fmul_rn(__fmul_rn(v.x, rstd), f.x)));
+          yv[2 * j + 1] = Elem<DT>::to_float(Elem<DT>::from_float(__fmul_rn(__fmul_rn(v.y, rstd), f.y)));
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) yv[j] = v[i][j];
+        for (int j = 0; j < 4; ++j) {
+          const float2 v = Elem<DT>::unpack(xw[j]);
+          yv[2 * j] = v.x;
+          yv[2 * j + 1] = v.y;
+        }
       }
       uint32_t out[4];
       if (rotate) {
@@ -116,13 +124,104 @@ __global__ void __launch_bounds__(kNormThreads) qk_norm_rope_kernel(const va_nor
   }
 }
 
+template <int DT>
+int launch_rows_dt(const va_norm_rope_args& a, cudaStream_t stream) {
+  const int64_t rows = (int64_t)a.batch * a.seq_len;
+  const int pieces = (a.heads > a.kv_heads ? a.heads : a.kv_heads) * kHeadDim / 8;  // of the wider of the two tensors
+  const int W = (pieces + 32 * NP - 1) / (32 * NP);                                 // 1 .. 8 (hidden sizes up to 8192)
+  const int per = 8 / W;
+  dim3 grid((unsigned)((rows + per - 1) / per), 2, 1);
+  qk_norm_rope_rows_kernel<DT><<<grid, 32 * W * per, 0, stream>>>(a, rows, W, per);
+  return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
+}
+
+// ---- the per-head form (HunyuanVideo): tensors are (B, H, L, 128) already ---------------------------------------
+// RMSNorm over the 128 elements of every (batch, head, token) row (eval/DiTEvalKit/kernels/include/norm/
+// narrow_rms_norm.cuh:22-73: sixteen threads per row, eight elements each, sum of squares in element order, xor
+// shuffles 8-4-2-1, rsqrtf(sum / 128 + eps), y = T((x * r) * w)), then the rotary embedding on interleaved pairs
+// in fp32 with per-element tables, out[i] = y[i] cos[i] + (i even ? -y[i+1] : y[i-1]) sin[i]
+// (eval/DiTEvalKit/kernels/include/rope/rope_enc_txtlast.cuh:32-76: tokens from rope_len on are left alone).
+// The same sixteen-threads-per-row layout here, sixteen rows per CTA.
+template <int DT>
+__global__ void __launch_bounds__(256) qk_head_norm_rope_kernel(const va_head_norm_rope_args a, int64_t q_rows, int64_t total_rows) {
+  using T = typename Elem<DT>::T;
+  const int lane16 = threadIdx.x & 15;
+  const int64_t row = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
+  const bool live = row < total_rows;
+  const bool is_k = live && row >= q_rows;
+  const int64_t r = live ? (is_k ? row - q_rows : row) : 0;
+  const int heads = is_k ? a.kv_heads : a.heads;
+  const int l = (int)(r % a.seq_len);
+  const int64_t bh = r / a.seq_len;
+  const int h = (int)(bh % heads), b = (int)(bh / heads);
+  const va_tensor4& in = is_k ? a.k : a.q;
+  const va_tensor4_out& out = is_k ? a.k_out : a.q_out;
+  const T* x = static_cast<const T*>(in.ptr) + b * in.stride_b + h * in.stride_h + (int64_t)l * in.stride_s + lane16 * 8;
+  T* y = static_cast<T*>(out.ptr) + b * out.stride_b + h * out.stride_h + (int64_t)l * out.stride_s + lane16 * 8;
+  const T* w = static_cast<const T*>(is_k ? a.k_weight : a.q_weight);
+
+  float v[8];
+  float ss = 0.f;
+  {
+    const uint4 raw = live ? __ldg(reinterpret_cast<const uint4*>(x)) : make_uint4(0, 0, 0, 0);
+    const uint32_t ww[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = Elem<DT>::unpack(ww[j]);
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+      ss = fmaf(f.x, f.x, ss);
+      ss = fmaf(f.y, f.y, ss);
+    }
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // within the row's sixteen lanes
+  if (w) {
+    const float rs = rsqrtf(ss / (float)kHeadDim + a.eps);
+    const uint4 wr = __ldg(reinterpret_cast<const uint4*>(w + lane16 * 8));
+    const uint32_t ww[4] = {wr.x, wr.y, wr.z, wr.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = Elem<DT>::unpack(ww[j]);
+      v[2 * j] = Elem<DT>::to_float(Elem<DT>::from_float(__fmul_rn(__fmul_rn(v[2 * j], rs), f.x)));
+      v[2 * j + 1] = Elem<DT>::to_float(Elem<DT>::from_float(__fmul_rn(__fmul_rn(v[2 * j + 1], rs), f.y)));
+    }
+  }
+  uint32_t o4[4];
+  if (a.cos != nullptr && l < a.rope_len) {
+    const float* cr = a.cos + (int64_t)l * kHeadDim + lane16 * 8;
+    const float* sr = a.sin + (int64_t)l * kHeadDim + lane16 * 8;
+    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cr)), c1 = __ldg(reinterpret_cast<const float4*>(cr + 4));
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(sr)), s1 = __ldg(reinterpret_cast<const float4*>(sr + 4));
+    const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float e = v[2 * j], od = v[2 * j + 1];
+      const float r0 = fmaf(-od, sn[2 * j], __fmul_rn(e, cc[2 * j]));        // x[i] cos[i] + (-x[i+1]) sin[i]
+      const float r1 = fmaf(e, sn[2 * j + 1], __fmul_rn(od, cc[2 * j + 1]));  // x[i] cos[i] + x[i-1] sin[i]
+      o4[j] = Elem<DT>::pack(r0, r1);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o4[j] = Elem<DT>::pack(v[2 * j], v[2 * j + 1]);
+  }
+  if (live) *reinterpret_cast<uint4*>(y) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+}
+
 }  // namespace
 
-int qk_norm_rope(const va_norm_rope_args& a, cudaStream_t stream) {
-  dim3 grid((unsigned)((int64_t)a.batch * a.seq_len), 2, 1);
-  if (a.dtype == VA_BF16) qk_norm_rope_kernel<VA_BF16><<<grid, kNormThreads, 0, stream>>>(a);
-  else qk_norm_rope_kernel<VA_FP16><<<grid, kNormThreads, 0, stream>>>(a);
+int qk_head_norm_rope(const va_head_norm_rope_args& a, cudaStream_t stream) {
+  const int64_t q_rows = (int64_t)a.batch * a.heads * a.seq_len, k_rows = (int64_t)a.batch * a.kv_heads * a.seq_len;
+  const int64_t total = q_rows + k_rows;
+  const unsigned grid = (unsigned)((total + 15) / 16);
+  if (a.dtype == VA_BF16) qk_head_norm_rope_kernel<VA_BF16><<<grid, 256, 0, stream>>>(a, q_rows, total);
+  else qk_head_norm_rope_kernel<VA_FP16><<<grid, 256, 0, stream>>>(a, q_rows, total);
   return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
+}
+
+int qk_norm_rope(const va_norm_rope_args& a, cudaStream_t stream) {
+  return a.dtype == VA_BF16 ? launch_rows_dt<VA_BF16>(a, stream) : launch_rows_dt<VA_FP16>(a, stream);
 }
 
 }  // namespace va

@@ -12,7 +12,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib as L
-from .api import VecAttentionArgumentError, _check, _dtype_code, _require_cuda, _stream
+from .api import VecAttentionArgumentError, _check, _dtype_code, _require_cuda, _rows_ok, _stream, _t4
 
 
 def as_heads(x: torch.Tensor, heads: int) -> torch.Tensor:
@@ -55,3 +55,39 @@ def qk_norm_rope(query: torch.Tensor, key: torch.Tensor, q_weight: Optional[torc
     with torch.cuda.device(dev):
         _check(L.lib().va_qk_norm_rope(C.byref(args), _stream()))
     return as_heads(q_out, heads), as_heads(k_out, kv_heads)
+
+
+def qk_head_norm_rope(query: torch.Tensor, key: torch.Tensor, q_weight: Optional[torch.Tensor],
+                      k_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor] = None,
+                      sin: Optional[torch.Tensor] = None, txt_len: int = 0, *, inplace: bool = False
+                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The per-head form of the preparation (HunyuanVideo, eval/DiTEvalKit/models/hyvideo/attention.py:187-213):
+    ``query`` (B, H, L, 128) and ``key`` (B, Hkv, L, 128) get an RMSNorm over their 128 elements with weights of
+    128 elements (``None``: no norm), then the rotary embedding on interleaved pairs with per-element float32
+    tables ``cos`` / ``sin`` (L - txt_len, 128) on all but the last ``txt_len`` tokens (``None``: no rotation).
+    One pass; ``inplace=True`` overwrites the inputs.  Returns (query, key) in the same (B, H, L, 128) layout."""
+    dev = _require_cuda(query, key)
+    b, h, l, d = query.shape
+    hkv = key.shape[1]
+    if d != 128 or key.shape[0] != b or key.shape[2] != l or key.shape[3] != 128 or query.dtype != key.dtype:
+        raise VecAttentionArgumentError("query / key must be (B, H, L, 128) and (B, Hkv, L, 128) of one dtype")
+    query, key = _rows_ok(query), _rows_ok(key)
+    q_out = query if inplace else torch.empty_like(query, memory_format=torch.contiguous_format)
+    k_out = key if inplace else torch.empty_like(key, memory_format=torch.contiguous_format)
+    for w in (q_weight, k_weight):
+        if w is not None and (w.dtype != query.dtype or w.numel() != 128 or not w.is_contiguous()):
+            raise VecAttentionArgumentError("norm weights must be contiguous, of 128 elements and of the tensors' dtype")
+    if (cos is None) != (sin is None):
+        raise VecAttentionArgumentError("give both rotary tables or neither")
+    rope_len = max(0, l - int(txt_len)) if cos is not None else 0
+    if cos is not None:
+        for f in (cos, sin):
+            if f.dtype != torch.float32 or f.dim() != 2 or f.shape[0] < rope_len or f.shape[1] != 128 or not f.is_contiguous():
+                raise VecAttentionArgumentError(f"rotary tables must be contiguous float32 of shape (>= {rope_len}, 128)")
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    args = L.HeadNormRopeArgs(_dtype_code(query), b, l, h, hkv, rope_len, _t4(query), _t4(key), _t4(q_out), _t4(k_out),
+                              ptr(q_weight), ptr(k_weight), float(eps), ptr(cos), ptr(sin))
+    with torch.cuda.device(dev):
+        _check(L.lib().va_qk_head_norm_rope(C.byref(args), _stream()))
+    return q_out, k_out
+
