@@ -436,8 +436,24 @@ def _pre_attention_leg(wl, peaks):
     ms = time_cuda(f, 2, 5)
     nbytes = 2 * (q.numel() + k.numel()) * 2 + 2 * cos.numel() * 4
     del qo, ko
-    return {"kernel": "qk_norm_rope_kernel", "ms": ms, "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
-            "peak": peaks["hbm_gbs"], "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+    res = {"kernel": "qk_norm_rope_rows_kernel", "ms": ms, "achieved": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
+           "peak": peaks["hbm_gbs"], "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+    # the per-head form on (B,H,L,128) tensors of the same size (per-element tables, text tokens last)
+    from vecattention_b200.preattn import qk_head_norm_rope
+    qh = q.view(wl.batch, wl.seq_len, wl.heads, D).transpose(1, 2).contiguous()
+    kh = k.view(wl.batch, wl.seq_len, wl.kv_heads, D).transpose(1, 2).contiguous()
+    del q, k
+    txt = 256
+    ang2 = torch.rand(wl.seq_len - txt, D, generator=g, device=dev) * 6.283
+    cos2, sin2 = torch.cos(ang2).contiguous(), torch.sin(ang2).contiguous()
+    wh = torch.ones(D, dtype=wl.dtype, device=dev)
+    f2 = lambda: qk_head_norm_rope(qh, kh, wh, wh, 1e-6, cos2, sin2, txt)
+    ms2 = time_cuda(f2, 2, 5)
+    nbytes2 = 2 * (qh.numel() + kh.numel()) * 2 + 2 * cos2.numel() * 4
+    res["per_head_form"] = {"kernel": "qk_head_norm_rope_kernel", "ms": ms2, "achieved": nbytes2 / (ms2 * 1e-3) / 1e9,
+                            "unit": "GB/s", "frac": nbytes2 / (ms2 * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                            "algorithmic_bytes": nbytes2}
+    return res
 
 
 def _measure(va, api, wl, thr, args, barrier, status, out):

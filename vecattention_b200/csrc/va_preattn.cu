@@ -141,82 +141,99 @@ int launch_rows_dt(const va_norm_rope_args& a, cudaStream_t stream) {
 // shuffles 8-4-2-1, rsqrtf(sum / 128 + eps), y = T((x * r) * w)), then the rotary embedding on interleaved pairs
 // in fp32 with per-element tables, out[i] = y[i] cos[i] + (i even ? -y[i+1] : y[i-1]) sin[i]
 // (eval/DiTEvalKit/kernels/include/rope/rope_enc_txtlast.cuh:32-76: tokens from rope_len on are left alone).
-// The same sixteen-threads-per-row layout here, sixteen rows per CTA.
+// The same sixteen-threads-per-row layout here.
 template <int DT>
-__global__ void __launch_bounds__(256) qk_head_norm_rope_kernel(const va_head_norm_rope_args a, int64_t q_rows, int64_t total_rows) {
+__global__ void __launch_bounds__(256) qk_head_norm_rope_kernel(const va_head_norm_rope_args a, int64_t tokens) {
   using T = typename Elem<DT>::T;
+  // Sixteen lanes per token (b, l); they walk the token's heads, Q's then K's, four at a time, so that the token's
+  // 1 KB of cos / sin entries is read once and four rows are in flight per lane.
   const int lane16 = threadIdx.x & 15;
-  const int64_t row = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
-  const bool live = row < total_rows;
-  const bool is_k = live && row >= q_rows;
-  const int64_t r = live ? (is_k ? row - q_rows : row) : 0;
-  const int heads = is_k ? a.kv_heads : a.heads;
-  const int l = (int)(r % a.seq_len);
-  const int64_t bh = r / a.seq_len;
-  const int h = (int)(bh % heads), b = (int)(bh / heads);
-  const va_tensor4& in = is_k ? a.k : a.q;
-  const va_tensor4_out& out = is_k ? a.k_out : a.q_out;
-  const T* x = static_cast<const T*>(in.ptr) + b * in.stride_b + h * in.stride_h + (int64_t)l * in.stride_s + lane16 * 8;
-  T* y = static_cast<T*>(out.ptr) + b * out.stride_b + h * out.stride_h + (int64_t)l * out.stride_s + lane16 * 8;
-  const T* w = static_cast<const T*>(is_k ? a.k_weight : a.q_weight);
-
-  float v[8];
-  float ss = 0.f;
-  {
-    const uint4 raw = live ? __ldg(reinterpret_cast<const uint4*>(x)) : make_uint4(0, 0, 0, 0);
-    const uint32_t ww[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = Elem<DT>::unpack(ww[j]);
-      v[2 * j] = f.x;
-      v[2 * j + 1] = f.y;
-      ss = fmaf(f.x, f.x, ss);
-      ss = fmaf(f.y, f.y, ss);
-    }
-  }
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // within the row's sixteen lanes
-  if (w) {
-    const float rs = rsqrtf(ss / (float)kHeadDim + a.eps);
-    const uint4 wr = __ldg(reinterpret_cast<const uint4*>(w + lane16 * 8));
-    const uint32_t ww[4] = {wr.x, wr.y, wr.z, wr.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = Elem<DT>::unpack(ww[j]);
-      v[2 * j] = Elem<DT>::to_float(Elem<DT>::from_float(__fmul_rn(__fmul_rn(v[2 * j], rs), f.x)));
-      v[2 * j + 1] = Elem<DT>::to_float(Elem<DT>::from_float(__fmul_rn(__fmul_rn(v[2 * j + 1], rs), f.y)));
-    }
-  }
-  uint32_t o4[4];
-  if (a.cos != nullptr && l < a.rope_len) {
+  const int64_t token = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
+  const bool live = token < tokens;
+  const int l = (int)((live ? token : 0) % a.seq_len);
+  const int b = (int)((live ? token : 0) / a.seq_len);
+  const bool rotate = a.cos != nullptr && l < a.rope_len;
+  float cc[8], sn[8];
+  if (rotate) {
     const float* cr = a.cos + (int64_t)l * kHeadDim + lane16 * 8;
     const float* sr = a.sin + (int64_t)l * kHeadDim + lane16 * 8;
     const float4 c0 = __ldg(reinterpret_cast<const float4*>(cr)), c1 = __ldg(reinterpret_cast<const float4*>(cr + 4));
     const float4 s0 = __ldg(reinterpret_cast<const float4*>(sr)), s1 = __ldg(reinterpret_cast<const float4*>(sr + 4));
-    const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float e = v[2 * j], od = v[2 * j + 1];
-      const float r0 = fmaf(-od, sn[2 * j], __fmul_rn(e, cc[2 * j]));        // x[i] cos[i] + (-x[i+1]) sin[i]
-      const float r1 = fmaf(e, sn[2 * j + 1], __fmul_rn(od, cc[2 * j + 1]));  // x[i] cos[i] + x[i-1] sin[i]
-      o4[j] = Elem<DT>::pack(r0, r1);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) o4[j] = Elem<DT>::pack(v[2 * j], v[2 * j + 1]);
+    cc[0] = c0.x; cc[1] = c0.y; cc[2] = c0.z; cc[3] = c0.w; cc[4] = c1.x; cc[5] = c1.y; cc[6] = c1.z; cc[7] = c1.w;
+    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
   }
-  if (live) *reinterpret_cast<uint4*>(y) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+#pragma unroll 1
+  for (int which = 0; which < 2; ++which) {  // 0: Q, 1: K
+    const va_tensor4& in = which ? a.k : a.q;
+    const va_tensor4_out& out = which ? a.k_out : a.q_out;
+    const int heads = which ? a.kv_heads : a.heads;
+    const T* w = static_cast<const T*>(which ? a.k_weight : a.q_weight);
+    const T* xb = static_cast<const T*>(in.ptr) + b * in.stride_b + (int64_t)l * in.stride_s + lane16 * 8;
+    T* yb = static_cast<T*>(out.ptr) + b * out.stride_b + (int64_t)l * out.stride_s + lane16 * 8;
+    float wv[8];
+    if (w) {
+      const uint4 wr = __ldg(reinterpret_cast<const uint4*>(w + lane16 * 8));
+      const uint32_t ww[4] = {wr.x, wr.y, wr.z, wr.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Elem<DT>::unpack(ww[j]);
+        wv[2 * j] = f.x;
+        wv[2 * j + 1] = f.y;
+      }
+    }
+#pragma unroll 1
+    for (int h0 = 0; h0 < heads; h0 += 4) {
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        raw[u] = (live && h0 + u < heads) ? __ldg(reinterpret_cast<const uint4*>(xb + (int64_t)(h0 + u) * in.stride_h)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t xw[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+        float v[8];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Elem<DT>::unpack(xw[j]);
+          v[2 * j] = f.x;
+          v[2 * j + 1] = f.y;
+          ss = fmaf(f.x, f.x, ss);
+          ss = fmaf(f.y, f.y, ss);
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // within the token's sixteen lanes
+        if (w) {
+          const float rs = rsqrtf(ss / (float)kHeadDim + a.eps);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = Elem<DT>::to_float(Elem<DT>::from_float(__fmul_rn(__fmul_rn(v[j], rs), wv[j])));
+        }
+        uint32_t o4[4];
+        if (rotate) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float e = v[2 * j], od = v[2 * j + 1];
+            const float r0 = fmaf(-od, sn[2 * j], __fmul_rn(e, cc[2 * j]));        // x[i] cos[i] + (-x[i+1]) sin[i]
+            const float r1 = fmaf(e, sn[2 * j + 1], __fmul_rn(od, cc[2 * j + 1]));  // x[i] cos[i] + x[i-1] sin[i]
+            o4[j] = Elem<DT>::pack(r0, r1);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o4[j] = Elem<DT>::pack(v[2 * j], v[2 * j + 1]);
+        }
+        if (live && h0 + u < heads)
+          *reinterpret_cast<uint4*>(yb + (int64_t)(h0 + u) * out.stride_h) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+      }
+    }
+  }
 }
 
 }  // namespace
 
 int qk_head_norm_rope(const va_head_norm_rope_args& a, cudaStream_t stream) {
-  const int64_t q_rows = (int64_t)a.batch * a.heads * a.seq_len, k_rows = (int64_t)a.batch * a.kv_heads * a.seq_len;
-  const int64_t total = q_rows + k_rows;
-  const unsigned grid = (unsigned)((total + 15) / 16);
-  if (a.dtype == VA_BF16) qk_head_norm_rope_kernel<VA_BF16><<<grid, 256, 0, stream>>>(a, q_rows, total);
-  else qk_head_norm_rope_kernel<VA_FP16><<<grid, 256, 0, stream>>>(a, q_rows, total);
+  const int64_t tokens = (int64_t)a.batch * a.seq_len;
+  const unsigned grid = (unsigned)((tokens + 15) / 16);
+  if (a.dtype == VA_BF16) qk_head_norm_rope_kernel<VA_BF16><<<grid, 256, 0, stream>>>(a, tokens);
+  else qk_head_norm_rope_kernel<VA_FP16><<<grid, 256, 0, stream>>>(a, tokens);
   return cudaGetLastError() == cudaSuccess ? VA_OK : VA_ERR_CUDA;
 }
 
