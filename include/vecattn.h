@@ -293,6 +293,7 @@ typedef struct {
 int va_qk_head_norm_rope(const va_head_norm_rope_args* args, va_stream_t stream);
 
 const char* va_status_string(int code);
+/* 100 * major + minor of this interface (201: va_attn_args gained the vision_* fields, va_qk_head_norm_rope added). */
 int va_version(void);
 
 #ifdef __cplusplus

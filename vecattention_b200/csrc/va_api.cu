@@ -92,7 +92,7 @@ using namespace va;
 
 extern "C" {
 
-int va_version(void) { return 200; }
+int va_version(void) { return 201; }  // 201: va_attn_args gained the vision fields; va_qk_head_norm_rope
 
 const char* va_status_string(int code) {
   switch (code) {
