@@ -17,7 +17,7 @@
 //              operand tile and rescales its part of the row of O in the rare chunks where the
 //              maximum moved.
 //   warps 8-11  K gather producers, warps 12-15 V gather producers: cp.async 16-byte pieces of the
-//              selected rows into rings of 128-byte-swizzled operand tiles (2 K stages, 3 V
+//              selected rows into rings of 128-byte-swizzled operand tiles (3 K stages, 2 V
 //              stages); copy completion is reported to the stage's mbarrier asynchronously; index
 //              loads run two chunks ahead and are exchanged inside the warp through shared memory.
 //   warps 16,17  MMA issuers (one thread each): warp 16 issues S_j = Q K_j^T, warp 17 issues
@@ -38,8 +38,8 @@ namespace {
 constexpr int kChunk = 128;
 constexpr int kKvTile = 128 * 256;  // 128 gathered rows
 constexpr int kQTile = 64 * 256;    // 64 query rows / 64 rows of P
-constexpr int kKStages = 2;  // K tiles are released as soon as S_j has been computed
-constexpr int kVStages = 3;  // V tiles live until O += P_j V_j has completed
+constexpr int kKStages = 3;  // K tiles are released as soon as S_j has been computed; the S issuer is the one that waits for data
+constexpr int kVStages = 2;  // V tiles live until O += P_j V_j has completed
 constexpr int kThreads = 576;
 // Registers per thread: the kernel is launched with 96 (the most 18 warps can all have); the two
 // producer warpgroups hand 40 each back and the two softmax warpgroups take them:
