@@ -54,6 +54,7 @@ struct SelectParams {
   int heads, kv_heads, rep, nq, sk;
   int pq, group_k_block;
   int nseg;           // CTAs per block of 128 rows, each writing the keep bits of one segment of the key range
+  int by_length;      // causal, whole row blocks per head: blockIdx.x lists the row blocks of all heads longest walk first
   int causal, wo_initial, compat_bsq, tile_offset, chunk_tiles;
 };
 
@@ -311,10 +312,19 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
   __shared__ WalkShared wsh;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int hkv = blockIdx.y, b = blockIdx.z;
+  int hkv = blockIdx.y;
+  const int b = blockIdx.z;
   const int nrows = p.rep * p.nq;
   // causal rows walk more keys the later their tile: the longest walks are started first
-  const int bx = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  int bx = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  if (p.by_length) {
+    // one grid row for all KV heads: CTAs are handed out in blockIdx.x order, so all heads' last 128 tiles come
+    // first, then all heads' last but one, ...: a longest-first schedule over the whole launch
+    const int blocks_per_head = p.nq / kRows, per_rank = p.rep * p.kv_heads;
+    const int rank = (int)blockIdx.x / per_rank, r2 = (int)blockIdx.x % per_rank;
+    hkv = r2 % p.kv_heads;
+    bx = (r2 / p.kv_heads) * blocks_per_head + (blocks_per_head - 1 - rank);
+  }
   const int row_base = (bx / p.nseg) * kRows, seg = bx % p.nseg;
 
   // ---- per-row limits: walker threads (warps 0-15) own row (warp % 4) * 32 + lane ----
@@ -525,6 +535,7 @@ int launch_bk(const SelectParams& p, const CUtensorMap& kmap, int batch, cudaStr
   // per-device attribute; setting it on every launch keeps multi-device processes correct
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess) return VA_ERR_CUDA;
   dim3 grid(p.rows_pad / kRows * p.nseg, p.kv_heads, batch);
+  if (p.by_length) grid = dim3(p.rows_pad / kRows * p.kv_heads, 1, batch);
   kern<<<grid, kThreads, kSmem, stream>>>(kmap, p);
   if (cudaGetLastError() != cudaSuccess) return VA_ERR_CUDA;
   const int64_t total_rows = (int64_t)batch * p.heads * p.nq;
@@ -592,6 +603,7 @@ int select(const va_select_args& a, cudaStream_t stream) {
     if (tiles < 64 * nseg) nseg = 1;  // short walks gain nothing
     p.nseg = nseg;
   }
+  p.by_length = (a.causal && p.nseg == 1 && a.nq % kRows == 0) ? 1 : 0;
   if (!a.workspace) return VA_ERR_NULL;
   if (a.workspace_bytes < select_workspace_bytes(a.batch, a.heads, a.kv_heads, a.nq, a.sk)) return VA_ERR_CAPACITY;
   if ((reinterpret_cast<uintptr_t>(a.workspace) & 15u) != 0) return VA_ERR_ALIGN;
