@@ -137,3 +137,29 @@ def test_config_sampled_tiles_match_oracle(va, name):
     print(f"{name}: max|cuda - oracle| {err.max():.3e}, mean {err.mean():.3e}; "
           f"mean|sparse - dense| oracle {e_ref / n:.4e}, cuda {e_gpu / n:.4e}")
     assert abs(e_ref - e_gpu) / n <= MEAN_ABS
+
+
+@pytest.mark.parametrize("causal,heads,kv_heads,nq,sk", [(False, 20, 20, 1024, 16384), (True, 12, 4, 256, 16384)])
+def test_selection_launch_schedules_agree(va, causal, heads, kv_heads, nq, sk):
+    """The selection kernel's grid depends on how many CTAs a launch has: key segments for few CTAs, the last
+    partial wave of equally long walks cut into segments, causal row blocks of all heads handed out longest walk
+    first.  One launch over all heads and one launch per KV group take different schedules and must produce the
+    same lists (the per-group form is the one the oracle and the reference's kernels are compared with)."""
+    from parity_util import membership
+    g = torch.Generator(device="cuda").manual_seed(17)
+    avg = torch.randn(1, heads, nq, 128, generator=g, device="cuda").to(torch.bfloat16)
+    k = torch.randn(1, kv_heads, sk, 128, generator=g, device="cuda").to(torch.bfloat16)
+    k[:, :, ::37] *= 3.0
+    gap = -math.log(0.6)
+    rep = heads // kv_heads
+    kw = dict(wo_initial=causal, group_k_block=8192, trim=False)
+    cnt_all, idx_all = va.fuse_qk_softmax_minp_wo_causal(avg, k, 0, gap, causal, 64, 16, **kw)
+    assert int(cnt_all.sum()) > 0
+    for kv in range(kv_heads):
+        hs = slice(kv * rep, (kv + 1) * rep)
+        cnt_g, idx_g = va.fuse_qk_softmax_minp_wo_causal(avg[:, hs].contiguous(), k[:, kv:kv + 1].contiguous(), 0, gap, causal,
+                                                         64, 16, **kw)
+        assert torch.equal(cnt_all[:, hs], cnt_g), f"KV group {kv}: counts differ between the two schedules"
+        a = membership(cnt_all[0, hs].reshape(-1), idx_all[0, hs].reshape(rep * nq, -1), sk)
+        b = membership(cnt_g[0].reshape(-1), idx_g[0].reshape(rep * nq, -1), sk)
+        assert torch.equal(a, b), f"KV group {kv}: selected keys differ between the two schedules"

@@ -55,6 +55,8 @@ struct SelectParams {
   int pq, group_k_block;
   int nseg;           // CTAs per block of 128 rows, each writing the keep bits of one segment of the key range
   int by_length;      // causal, whole row blocks per head: blockIdx.x lists the row blocks of all heads longest walk first
+  int tail_from, tail_seg;  // tail_seg > 0: a flat grid; the CTAs from number tail_from on (the last, partial wave of
+                            // equally long walks) are cut into tail_seg key segments each
   int causal, wo_initial, compat_bsq, tile_offset, chunk_tiles;
 };
 
@@ -313,7 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int hkv = blockIdx.y;
-  const int b = blockIdx.z;
+  int b = blockIdx.z;
   const int nrows = p.rep * p.nq;
   // causal rows walk more keys the later their tile: the longest walks are started first
   int bx = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
@@ -325,7 +327,25 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
     hkv = r2 % p.kv_heads;
     bx = (r2 / p.kv_heads) * blocks_per_head + (blocks_per_head - 1 - rank);
   }
-  const int row_base = (bx / p.nseg) * kRows, seg = bx % p.nseg;
+  int nseg = p.nseg;
+  int row_base = (bx / p.nseg) * kRows, seg = bx % p.nseg;
+  if (p.tail_seg > 0) {
+    // Equally long walks fill whole waves of SMs except for the last CTAs; those are cut into key segments so that
+    // the last wave is shorter (a segment's CTA re-walks the maxima of the segments before it, the cheap half).
+    const int lin = (int)blockIdx.x, nb = p.rows_pad / kRows;
+    int cta = lin;
+    seg = 0;
+    nseg = 1;
+    if (lin >= p.tail_from) {
+      const int r = lin - p.tail_from;
+      cta = p.tail_from + r / p.tail_seg;
+      seg = r % p.tail_seg;
+      nseg = p.tail_seg;
+    }
+    row_base = (cta % nb) * kRows;
+    hkv = (cta / nb) % p.kv_heads;
+    b = cta / (nb * p.kv_heads);
+  }
 
   // ---- per-row limits: walker threads (warps 0-15) own row (warp % 4) * 32 + lane ----
   const bool is_walker = warp < kWalkerWarps;
@@ -352,8 +372,8 @@ __global__ void __launch_bounds__(kThreads, 1) select_mask_kernel(const __grid_c
   // With few row blocks the key range is cut into segments, one CTA each: a CTA walks from the first tile (the
   // running maximum is a prefix quantity) but forms keep bits only for its own segment, and stops after it.
   int t_keep = t_lo;
-  if (p.nseg > 1) {
-    const int per = (t_hi - t_lo + p.nseg - 1) / p.nseg;
+  if (nseg > 1) {
+    const int per = (t_hi - t_lo + nseg - 1) / nseg;
     t_keep = t_lo + seg * per;
     if (t_keep >= t_hi) return;
     t_hi = min(t_hi, t_keep + per);
@@ -536,6 +556,10 @@ int launch_bk(const SelectParams& p, const CUtensorMap& kmap, int batch, cudaStr
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess) return VA_ERR_CUDA;
   dim3 grid(p.rows_pad / kRows * p.nseg, p.kv_heads, batch);
   if (p.by_length) grid = dim3(p.rows_pad / kRows * p.kv_heads, 1, batch);
+  if (p.tail_seg > 0) {
+    const int ctas = p.rows_pad / kRows * p.kv_heads * batch;
+    grid = dim3(p.tail_from + (ctas - p.tail_from) * p.tail_seg, 1, 1);
+  }
   kern<<<grid, kThreads, kSmem, stream>>>(kmap, p);
   if (cudaGetLastError() != cudaSuccess) return VA_ERR_CUDA;
   const int64_t total_rows = (int64_t)batch * p.heads * p.nq;
@@ -604,6 +628,17 @@ int select(const va_select_args& a, cudaStream_t stream) {
     p.nseg = nseg;
   }
   p.by_length = (a.causal && p.nseg == 1 && a.nq % kRows == 0) ? 1 : 0;
+  p.tail_from = p.tail_seg = 0;
+  if (!a.causal && p.nseg == 1) {  // equally long walks: shorten the last, partial wave
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t ctas = (int64_t)(p.rows_pad / kRows) * a.kv_heads * a.batch;
+    const int64_t full = ctas / sms * sms, rest = ctas - full;
+    if (full > 0 && rest > 0 && rest * 2 <= sms && (a.sk + kTile - 1) / kTile >= 128 && ctas < (1 << 30)) {
+      p.tail_from = (int)full;
+      p.tail_seg = (int)(sms / rest < 4 ? sms / rest : 4);
+    }
+  }
   if (!a.workspace) return VA_ERR_NULL;
   if (a.workspace_bytes < select_workspace_bytes(a.batch, a.heads, a.kv_heads, a.nq, a.sk)) return VA_ERR_CAPACITY;
   if ((reinterpret_cast<uintptr_t>(a.workspace) & 15u) != 0) return VA_ERR_ALIGN;
